@@ -1,0 +1,252 @@
+/*
+ * opsgnn_b200.h — C ABI of the B200 (sm_100a) kernels behind the ops_gnn sparse
+ * message-passing operators.
+ *
+ * Every entry point takes raw device pointers, plain sizes and a CUDA stream
+ * (passed as void*), enqueues its work on that stream and returns without
+ * synchronising.  The return value is 0 on success, a positive cudaError_t when
+ * a CUDA call failed, or one of the negative OPSGNN_ERR_* codes when the
+ * arguments were rejected before anything was launched.  Nothing throws across
+ * this boundary, nothing here allocates device memory: scratch is passed in by
+ * the caller and sized by the *_workspace_bytes / *_plan_bytes queries.
+ *
+ * The citations "replaces <file>:<line>" name the launcher of the reference
+ * project (Atlas-Ascend-Fork/ops-gnn, paths relative to its root) that the
+ * entry point stands in for.
+ */
+#ifndef OPSGNN_B200_H
+#define OPSGNN_B200_H
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define OPSGNN_API __attribute__((visibility("default")))
+#else
+#define OPSGNN_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define OPSGNN_OK 0
+#define OPSGNN_ERR_INVALID (-1)     /* bad shape / null pointer / bad enum     */
+#define OPSGNN_ERR_UNSUPPORTED (-2) /* dtype or mode combination not built     */
+#define OPSGNN_ERR_WORKSPACE (-3)   /* workspace too small or misaligned       */
+#define OPSGNN_ERR_LIMIT (-4)       /* size beyond a documented fixed maximum  */
+
+/* ---- dtype ids (0..4 as csrc/npu/torch_sparse_spmm/op_host/torch_sparse_spmm.cpp:19-36) */
+#define OPSGNN_F32 0
+#define OPSGNN_F16 1
+#define OPSGNN_BF16 2
+#define OPSGNN_I8 3
+#define OPSGNN_I32 4
+#define OPSGNN_I64 5
+#define OPSGNN_U8 6
+#define OPSGNN_I16 7
+#define OPSGNN_F64 8
+
+/* ---- reductions of the CSR engine -------------------------------------- */
+#define OPSGNN_REDUCE_SUM 0
+#define OPSGNN_REDUCE_MEAN 1
+#define OPSGNN_REDUCE_MIN 2
+#define OPSGNN_REDUCE_MAX 3
+#define OPSGNN_REDUCE_LOGSUMEXP 4
+
+/* ---- extremum rules (who wins, what NaN does) --------------------------- */
+/* first edge among ties, NaN never selected, row without a selectable value
+ * gives 0 and arg = arg_none (torch_sparse_spmm_kernel.h:56-67). */
+#define OPSGNN_EXTREMUM_IGNORE_NAN 0
+/* first occurrence among ties, the first NaN wins and sticks (torch.min/max and
+ * scatter_reduce_(amin/amax) behaviour used by the segment_csr and spmm goldens). */
+#define OPSGNN_EXTREMUM_PROPAGATE_NAN 1
+/* strict compare against a +/-finite-max seed: NaN and values not better than
+ * the seed never win; an unbeaten seed gives 0 (test/segment_coo/arch35/golden.py:42-58,132-148). */
+#define OPSGNN_EXTREMUM_SEEDED 2
+
+OPSGNN_API const char* opsgnn_status_string(int status);
+/* Number of SMs of the current device (replaces ResolveAivCoreNum,
+ * csrc/npu/common/aiv_launch_utils.h:22-37). */
+OPSGNN_API int opsgnn_sm_count(int* count);
+
+/* ======================================================================== */
+/* CSR reduce engine: SpMM, segment_csr, segment_coo, segment_logsumexp      */
+/* ======================================================================== */
+
+/*
+ * out[b, r, k] = reduce over e in [ptr[r], ptr[r+1]) of  w(e,k) * mat[b, col(e), k]
+ *
+ * col == NULL means col(e) = e (a segment reduction over consecutive rows of
+ * mat); val == NULL means w = 1.  The work is split into equal shares of
+ * (edges + row ends) by a merge-path plan, so a row with millions of edges is
+ * spread over many thread blocks; partial rows are recombined in a fixed order
+ * (results are bitwise reproducible).
+ */
+typedef struct OpsgnnCsrReduceDesc {
+    int64_t rows;        /* M: output rows / segments                              */
+    int64_t src_rows;    /* N: rows of mat (gather domain)                         */
+    int64_t feat;        /* K: features per row                                    */
+    int64_t nnz;         /* E: edges; with col == NULL must equal src_rows or less */
+    int64_t batches;     /* B: leading batch count of mat/out (>= 1)               */
+    int64_t value_width; /* 0 (val NULL), 1 (one weight per edge) or K             */
+    int64_t arg_none;    /* arg written where no element was selected              */
+    int32_t reduce;      /* OPSGNN_REDUCE_*                                        */
+    int32_t extremum;    /* OPSGNN_EXTREMUM_* (min/max only)                       */
+    int32_t ptr_type;    /* OPSGNN_I32 or OPSGNN_I64: dtype of ptr                 */
+    int32_t col_type;    /* OPSGNN_I32 or OPSGNN_I64: dtype of col (ignored if NULL)*/
+    int32_t in_type;     /* dtype of mat and val                                   */
+    int32_t out_type;    /* dtype of out                                           */
+} OpsgnnCsrReduceDesc;
+
+/* Bytes of the merge-path plan for a CSR structure with `rows` rows and `nnz` edges. */
+OPSGNN_API int opsgnn_csr_plan_bytes(int64_t rows, int64_t nnz, int64_t* bytes);
+/* Builds the plan (one binary search per thread block of the reduce kernel).  It
+ * depends on ptr only and may be reused for every call on the same graph. */
+OPSGNN_API int opsgnn_csr_plan_build(const void* ptr, int ptr_type, int64_t rows, int64_t nnz, void* plan, void* stream);
+/* Bytes of carry scratch needed by opsgnn_csr_reduce for this descriptor. */
+OPSGNN_API int opsgnn_csr_reduce_workspace_bytes(const OpsgnnCsrReduceDesc* desc, int64_t* bytes);
+/*
+ * Replaces TorchSparseSpmm (csrc/npu/torch_sparse_spmm/op_kernel/arch35/torch_sparse_spmm.cpp:38-57),
+ * SpmmSum/SpmmMax/SpmmMin and UnifiedSpmm (csrc/npu/common/spmm/spmm_utils.h:156-186,
+ * csrc/npu/unified_spmm/op_host/unified_spmm.cpp:116-158), SegmentCsr
+ * (csrc/npu/segment_csr/op_kernel/arch35/segment_csr.h:132-139), the reduction half of SegmentCoo
+ * (csrc/npu/segment_coo/op_kernel/arch35/segment_coo.h:13-14) and the segment_logsumexp launch
+ * (csrc/npu/segment_logsumexp/op_host/segment_logsumexp.cpp:133-168).
+ * arg (int64, same shape as out) is required for min/max and ignored otherwise.
+ */
+OPSGNN_API int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* ptr, const void* col, const void* val,
+                      const void* mat, void* out, int64_t* arg, const void* plan, void* workspace,
+                      int64_t workspace_bytes, void* stream);
+
+/* Typed mean for integer sums (count wraps to the value dtype, truncating division, zero count gives 0):
+ * out[b, r, k] /= narrow(ptr[r+1]-ptr[r]).  Follows MeanDivideRounded,
+ * csrc/npu/segment_csr/op_kernel/arch35/segment_csr.cpp:282-297. */
+OPSGNN_API int opsgnn_csr_integer_mean(void* out, int out_type, const void* ptr, int ptr_type, int64_t rows, int64_t feat,
+                            int64_t batches, void* stream);
+
+/* ======================================================================== */
+/* SDDMM on CSR                                                              */
+/* ======================================================================== */
+#define OPSGNN_SDDMM_DOT 0
+#define OPSGNN_SDDMM_ADD 1
+#define OPSGNN_SDDMM_SUB 2
+#define OPSGNN_SDDMM_MUL 3
+#define OPSGNN_SDDMM_DIV 4
+#define OPSGNN_SDDMM_COPY_LHS 5
+#define OPSGNN_SDDMM_COPY_RHS 6
+/* operand targets: which index of edge e selects the operand row */
+#define OPSGNN_TARGET_ROW 0  /* "u"/"src": CSR row of e  */
+#define OPSGNN_TARGET_EDGE 1 /* "e": e itself            */
+#define OPSGNN_TARGET_COL 2  /* "v"/"dst": indices[e]    */
+
+typedef struct OpsgnnSddmmDesc {
+    int64_t rows;      /* CSR rows                                   */
+    int64_t nnz;       /* edges                                      */
+    int64_t feat;      /* output feature width (dot: reduction width) */
+    int64_t lhs_feat;  /* 1 (broadcast) or feat                      */
+    int64_t rhs_feat;  /* 1 (broadcast) or feat                      */
+    int32_t op;        /* OPSGNN_SDDMM_*                              */
+    int32_t lhs_target;
+    int32_t rhs_target;
+    int32_t index_type; /* OPSGNN_I32 / OPSGNN_I64 (indptr and indices) */
+    int32_t dtype;      /* OPSGNN_F32 / OPSGNN_F16 / OPSGNN_BF16        */
+} OpsgnnSddmmDesc;
+
+/* Replaces SddmmCsr (csrc/npu/sddmm_csr/op_kernel/arch22/sddmm_csr.cpp) as launched by
+ * LaunchSddmmCsr (csrc/npu/sddmm_csr/op_host/sddmm_csr.cpp:368-411).
+ * dot writes out[nnz]; the other ops write out[nnz, feat].  fp16/bf16 compute in fp32. */
+OPSGNN_API int opsgnn_sddmm_csr(const OpsgnnSddmmDesc* desc, const void* indptr, const void* indices, const void* lhs,
+                     const void* rhs, void* out, void* stream);
+
+/* dvalue[e, w] = sum_b sum_k mat[b, col[e], k] * grad[b, row(e), k]  (w = 0 when width == 1, else k).
+ * Replaces TorchSparseSpmmValueGrad (csrc/npu/torch_sparse_spmm/op_kernel/arch35/torch_sparse_spmm_kernel.h:326-395).
+ * mean == 1 divides by the row's edge count.  grad and out are fp32; mat has dtype mat_type. */
+OPSGNN_API int opsgnn_spmm_value_grad(const int64_t* ptr, const int64_t* col, const void* mat, int mat_type, const float* grad,
+                           float* out, int64_t rows, int64_t src_rows, int64_t feat, int64_t nnz, int64_t batches,
+                           int64_t width, int mean, void* stream);
+
+/* ======================================================================== */
+/* index conversions and CSR support kernels                                 */
+/* ======================================================================== */
+/* ptr[i] = number of ind[] entries < i, i in [0, rows]; ind sorted.  Replaces Ind2Ptr
+ * (csrc/npu/ind2ptr/op_kernel/arch35/ind2ptr.cpp:146-168) and ConvertKernel with toPtr
+ * (torch_sparse_spmm_kernel.h:432-456). */
+OPSGNN_API int opsgnn_ind2ptr(const int64_t* ind, int64_t nnz, int64_t* ptr, int64_t rows, void* stream);
+/* ind[e] = row r with ptr[r] <= e < ptr[r+1].  Replaces Ptr2Ind (csrc/npu/ptr2ind/op_kernel/arch35/ptr2ind.cpp:20-52). */
+OPSGNN_API int opsgnn_ptr2ind(const int64_t* ptr, int64_t rows, int64_t* ind, int64_t nnz, void* stream);
+/* status[0] = 0 valid, 1 bad pointer array, 2 column out of range (maximum over the structure).
+ * Replaces TorchSparseSpmmValidate (torch_sparse_spmm_kernel.h:399-430).  index_type selects int32/int64. */
+OPSGNN_API int opsgnn_csr_validate(const void* ptr, const void* col, int index_type, int64_t rows, int64_t cols, int64_t nnz,
+                        int32_t* status, void* stream);
+/* out[i, :] = value[perm[i], :].  Replaces TorchSparseSpmmPermuteValues (torch_sparse_spmm.cpp:16-36). */
+OPSGNN_API int opsgnn_permute_values(const int64_t* perm, const void* value, void* out, int64_t rows, int64_t width,
+                          int elem_bytes, void* stream);
+/* stats[0] = min(index), stats[1] = max(index), stats[2] = 1 when index is non-decreasing else 0.
+ * One pass that serves the bounds checks of the grouped-softmax and scatter wrappers
+ * (python/ops_gnn/_grouped_softmax.py:67-79, python/ops_gnn/scatter.py:347-361).  index_type I32/I64. */
+OPSGNN_API int opsgnn_index_stats(const void* index, int index_type, int64_t n, int64_t* stats, void* stream);
+
+/* ======================================================================== */
+/* scatter (unsorted index)                                                  */
+/* ======================================================================== */
+#define OPSGNN_SCATTER_SUM 0
+#define OPSGNN_SCATTER_MUL 1
+#define OPSGNN_SCATTER_MEAN 2
+#define OPSGNN_SCATTER_MIN 3
+#define OPSGNN_SCATTER_MAX 4
+
+typedef struct OpsgnnScatterDesc {
+    int64_t before;     /* product of dims before `dim`                       */
+    int64_t dim_len;    /* src.size(dim)                                      */
+    int64_t after;      /* product of dims after `dim`                        */
+    int64_t out_len;    /* out.size(dim)                                      */
+    int64_t index_full; /* 0: index is [dim_len]; 1: index has src's shape    */
+    int32_t reduce;     /* OPSGNN_SCATTER_* (codes of scatter_tiling.h:14-20) */
+    int32_t dtype;      /* src/out dtype                                      */
+    int32_t has_out;    /* out holds caller data that takes part in the reduce */
+} OpsgnnScatterDesc;
+
+OPSGNN_API int opsgnn_scatter_workspace_bytes(const OpsgnnScatterDesc* desc, int64_t* bytes);
+/* Replaces the Scatter launcher (csrc/npu/scatter/op_kernel/arch35/scatter.cpp) called from scatter_forward
+ * (csrc/npu/scatter/op_host/scatter.cpp:242-267).  out must be pre-filled by the caller exactly as the reference's
+ * Python front-end does (zeros / ones / dtype extrema or the user's out); arg (int64) is required for min/max and
+ * receives the largest source position among ties, dim_len where nothing was written. */
+OPSGNN_API int opsgnn_scatter(const OpsgnnScatterDesc* desc, const void* src, const int64_t* index, void* out, int64_t* arg,
+                   void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ======================================================================== */
+/* grouped softmax family (unsorted 1-D index along `dim`)                   */
+/* ======================================================================== */
+#define OPSGNN_GROUPED_SOFTMAX 0
+#define OPSGNN_GROUPED_LOG_SOFTMAX 1
+#define OPSGNN_GROUPED_LOGSUMEXP 2
+
+typedef struct OpsgnnGroupedDesc {
+    int64_t batch;   /* product of dims before `dim`          */
+    int64_t dim_len; /* src.size(dim)                         */
+    int64_t after;   /* product of dims after `dim`           */
+    int64_t groups;  /* dim_size                              */
+    int32_t mode;    /* OPSGNN_GROUPED_*                      */
+    int32_t dtype;   /* F32 / F16 / BF16                      */
+    int32_t sorted;  /* 1: index is non-decreasing (enables the single-sweep path) */
+} OpsgnnGroupedDesc;
+
+OPSGNN_API int opsgnn_grouped_workspace_bytes(const OpsgnnGroupedDesc* desc, int64_t* bytes);
+/* Replaces ScatterSoftmaxForward / ScatterLogSoftmaxForward / ScatterLogSumExpForward
+ * (csrc/npu/scatter_softmax/op_kernel/common/scatter_softmax_kernel_entry.h:218-283) as launched by
+ * grouped_softmax::RunForward (csrc/npu/scatter_softmax/common/grouped_softmax_shared.h:178-208).
+ * index is int32 [dim_len]. out has src's shape (softmax, log_softmax) or [batch, groups, after] (logsumexp). */
+OPSGNN_API int opsgnn_grouped_forward(const OpsgnnGroupedDesc* desc, const void* src, const int32_t* index, void* out,
+                           void* workspace, int64_t workspace_bytes, void* stream);
+/* Replaces the backward launches (scatter_softmax_kernel_entry.h:247-264, 293-357; RunBackward
+ * grouped_softmax_shared.h:212-248).  softmax: grad = out*(g - sum_group(out*g)); log_softmax:
+ * grad = g - exp(out)*sum_group(g); logsumexp: grad = exp(src - out[group]) * g[group] (src required). */
+OPSGNN_API int opsgnn_grouped_backward(const OpsgnnGroupedDesc* desc, const void* src, const void* out, const void* grad_out,
+                            const int32_t* index, void* grad_src, void* workspace, int64_t workspace_bytes,
+                            void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OPSGNN_B200_H */

@@ -1,0 +1,309 @@
+// C ABI of the CSR reduce engine: plan construction, scratch sizing and dtype dispatch.
+#include "csr_instances.h"
+
+namespace opsgnn {
+namespace csr {
+namespace {
+
+bool IsIndexType(int t) { return t == OPSGNN_I32 || t == OPSGNN_I64; }
+
+int AccBytes(int in_type)
+{
+    switch (in_type) {
+        case OPSGNN_F64:
+        case OPSGNN_I64:
+            return 8;
+        default:
+            return 4;
+    }
+}
+
+int KindOf(int reduce)
+{
+    switch (reduce) {
+        case OPSGNN_REDUCE_SUM:
+        case OPSGNN_REDUCE_MEAN:
+            return kSum;
+        case OPSGNN_REDUCE_MIN:
+        case OPSGNN_REDUCE_MAX:
+            return kExtremum;
+        case OPSGNN_REDUCE_LOGSUMEXP:
+            return kLogSumExp;
+        default:
+            return -1;
+    }
+}
+
+// Upper bound of a carry row: every feature tile is padded to at most 256 features.
+int64_t CarryWidth(const OpsgnnCsrReduceDesc& d) { return d.batches * AlignUp(d.feat > 0 ? d.feat : 1, 256); }
+
+int CheckDesc(const OpsgnnCsrReduceDesc* d)
+{
+    if (d == nullptr || d->rows < 0 || d->src_rows < 0 || d->feat < 0 || d->nnz < 0 || d->batches < 1) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (KindOf(d->reduce) < 0 || !IsIndexType(d->ptr_type)) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (d->value_width != 0 && d->value_width != 1 && d->value_width != d->feat) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (d->nnz > 0 && d->src_rows == 0) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (d->extremum < OPSGNN_EXTREMUM_IGNORE_NAN || d->extremum > OPSGNN_EXTREMUM_SEEDED) {
+        return OPSGNN_ERR_INVALID;
+    }
+    return OPSGNN_OK;
+}
+
+}  // namespace
+}  // namespace csr
+}  // namespace opsgnn
+
+using namespace opsgnn;
+using namespace opsgnn::csr;
+
+extern "C" int opsgnn_csr_plan_bytes(int64_t rows, int64_t nnz, int64_t* bytes)
+{
+    if (bytes == nullptr || rows < 0 || nnz < 0) {
+        return OPSGNN_ERR_INVALID;
+    }
+    *bytes = (NumCta(rows, nnz) + 1) * static_cast<int64_t>(sizeof(int64_t));
+    return OPSGNN_OK;
+}
+
+extern "C" int opsgnn_csr_plan_build(const void* ptr, int ptr_type, int64_t rows, int64_t nnz, void* plan, void* stream)
+{
+    if (ptr == nullptr || plan == nullptr || rows < 0 || nnz < 0 || !IsIndexType(ptr_type)) {
+        return OPSGNN_ERR_INVALID;
+    }
+    const int64_t num_cta = NumCta(rows, nnz);
+    const int threads = 256;
+    const unsigned grid = static_cast<unsigned>(CeilDiv(num_cta + 1, threads));
+    if (ptr_type == OPSGNN_I64) {
+        PlanKernel<int64_t><<<grid, threads, 0, AsStream(stream)>>>(static_cast<const int64_t*>(ptr), rows, nnz, num_cta,
+                                                                      static_cast<int64_t*>(plan));
+    } else {
+        PlanKernel<int32_t><<<grid, threads, 0, AsStream(stream)>>>(static_cast<const int32_t*>(ptr), rows, nnz, num_cta,
+                                                                      static_cast<int64_t*>(plan));
+    }
+    return LaunchStatus();
+}
+
+extern "C" int opsgnn_csr_reduce_workspace_bytes(const OpsgnnCsrReduceDesc* desc, int64_t* bytes)
+{
+    int status = CheckDesc(desc);
+    if (status != OPSGNN_OK || bytes == nullptr) {
+        return OPSGNN_ERR_INVALID;
+    }
+    const int64_t num_cta = NumCta(desc->rows, desc->nnz);
+    const int64_t width = CarryWidth(*desc);
+    int64_t total = AlignUp(num_cta * 8, 256);                        // carry_row
+    total += AlignUp(num_cta * width * AccBytes(desc->in_type), 256);  // carry_val
+    if (KindOf(desc->reduce) == kExtremum) {
+        total += AlignUp(num_cta * width * 8, 256);  // carry_arg
+    }
+    *bytes = total;
+    return OPSGNN_OK;
+}
+
+extern "C" int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* ptr, const void* col, const void* val,
+                                 const void* mat, void* out, int64_t* arg, const void* plan, void* workspace,
+                                 int64_t workspace_bytes, void* stream)
+{
+    int status = CheckDesc(desc);
+    if (status != OPSGNN_OK) {
+        return status;
+    }
+    const OpsgnnCsrReduceDesc& d = *desc;
+    if (d.rows == 0 || d.feat == 0) {
+        return OPSGNN_OK;
+    }
+    const int kind = KindOf(d.reduce);
+    if (ptr == nullptr || out == nullptr || plan == nullptr || (d.nnz > 0 && mat == nullptr)) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (kind == kExtremum && arg == nullptr) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if ((d.value_width != 0) != (val != nullptr)) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (col != nullptr && (!IsIndexType(d.col_type) || d.col_type != d.ptr_type)) {
+        return OPSGNN_ERR_UNSUPPORTED;
+    }
+    if (col == nullptr && d.nnz > d.src_rows) {
+        return OPSGNN_ERR_INVALID;
+    }
+    int64_t needed = 0;
+    opsgnn_csr_reduce_workspace_bytes(desc, &needed);
+    if (workspace == nullptr || workspace_bytes < needed || !Aligned(workspace, 256)) {
+        return OPSGNN_ERR_WORKSPACE;
+    }
+
+    Params p{};
+    p.ptr = ptr;
+    p.col = col;
+    p.val = val;
+    p.mat = mat;
+    p.out = out;
+    p.arg = arg;
+    p.plan = static_cast<const int64_t*>(plan);
+    p.rows = d.rows;
+    p.src_rows = d.src_rows;
+    p.feat = d.feat;
+    p.nnz = d.nnz;
+    p.batches = d.batches;
+    p.arg_none = d.arg_none;
+    p.num_cta = NumCta(d.rows, d.nnz);
+    p.mean = d.reduce == OPSGNN_REDUCE_MEAN;
+    p.is_min = d.reduce == OPSGNN_REDUCE_MIN;
+    p.extremum = d.extremum;
+    p.has_val = val != nullptr;
+    p.wide = val != nullptr && d.value_width == d.feat && d.feat != 1;
+    char* cursor = static_cast<char*>(workspace);
+    const int64_t width = CarryWidth(d);
+    p.carry_row = reinterpret_cast<int64_t*>(cursor);
+    cursor += AlignUp(p.num_cta * 8, 256);
+    p.carry_val = cursor;
+    cursor += AlignUp(p.num_cta * width * AccBytes(d.in_type), 256);
+    p.carry_arg = reinterpret_cast<int64_t*>(cursor);
+
+    const bool index64 = d.ptr_type == OPSGNN_I64;
+    cudaStream_t s = AsStream(stream);
+    if (col != nullptr) {
+        switch (d.in_type) {
+            case OPSGNN_F32:
+                if (d.out_type != OPSGNN_F32) {
+                    return OPSGNN_ERR_UNSUPPORTED;
+                }
+                return RunSpmmF32(p, index64, kind, s);
+            case OPSGNN_F16:
+                if (d.out_type != OPSGNN_F16 && d.out_type != OPSGNN_F32) {
+                    return OPSGNN_ERR_UNSUPPORTED;
+                }
+                return RunSpmmF16(p, index64, kind, d.out_type == OPSGNN_F32, s);
+            case OPSGNN_BF16:
+                if (d.out_type != OPSGNN_BF16 && d.out_type != OPSGNN_F32) {
+                    return OPSGNN_ERR_UNSUPPORTED;
+                }
+                return RunSpmmBF16(p, index64, kind, d.out_type == OPSGNN_F32, s);
+            case OPSGNN_I8:
+                if (d.out_type != OPSGNN_I32 && d.out_type != OPSGNN_F32) {
+                    return OPSGNN_ERR_UNSUPPORTED;
+                }
+                return RunSpmmI8(p, index64, kind, d.out_type == OPSGNN_F32, s);
+            default:
+                return OPSGNN_ERR_UNSUPPORTED;
+        }
+    }
+    if (val != nullptr || d.out_type != d.in_type) {
+        return OPSGNN_ERR_UNSUPPORTED;
+    }
+    switch (d.in_type) {
+        case OPSGNN_F32:
+        case OPSGNN_F16:
+        case OPSGNN_BF16:
+            return RunSegmentFloat(p, d.in_type, index64, kind, s);
+        default:
+            return RunSegmentOther(p, d.in_type, index64, kind, s);
+    }
+}
+
+namespace opsgnn {
+namespace csr {
+template <class T, class PtrT>
+__global__ void IntegerMeanKernel(T* out, const PtrT* ptr, int64_t rows, int64_t feat, int64_t batches)
+{
+    const int64_t total = batches * rows * feat;
+    for (int64_t at = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; at < total;
+         at += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t row = (at / feat) % rows;
+        // The count is narrowed to the value dtype first (a 256-element uint8 segment has count 0 and mean 0).
+        const T count = static_cast<T>(static_cast<int64_t>(ptr[row + 1]) - static_cast<int64_t>(ptr[row]));
+        const T value = out[at];
+        T mean = T(0);
+        if (count != T(0)) {
+            if (std::is_signed<T>::value && count == T(-1)) {
+                mean = static_cast<T>(T(0) - value);  // avoids the INT_MIN / -1 trap, wraps like two's complement
+            } else {
+                mean = static_cast<T>(value / count);
+            }
+        }
+        out[at] = mean;
+    }
+}
+
+template <class T>
+int IntegerMean(void* out, const void* ptr, int ptr_type, int64_t rows, int64_t feat, int64_t batches, cudaStream_t s)
+{
+    const int64_t total = batches * rows * feat;
+    if (total == 0) {
+        return OPSGNN_OK;
+    }
+    const int threads = 256;
+    int64_t blocks = CeilDiv(total, threads);
+    const int64_t cap = static_cast<int64_t>(SmCount()) * 16;
+    blocks = blocks < cap ? blocks : cap;
+    if (ptr_type == OPSGNN_I64) {
+        IntegerMeanKernel<T, int64_t><<<static_cast<unsigned>(blocks), threads, 0, s>>>(
+            static_cast<T*>(out), static_cast<const int64_t*>(ptr), rows, feat, batches);
+    } else {
+        IntegerMeanKernel<T, int32_t><<<static_cast<unsigned>(blocks), threads, 0, s>>>(
+            static_cast<T*>(out), static_cast<const int32_t*>(ptr), rows, feat, batches);
+    }
+    return LaunchStatus();
+}
+}  // namespace csr
+}  // namespace opsgnn
+
+extern "C" int opsgnn_csr_integer_mean(void* out, int out_type, const void* ptr, int ptr_type, int64_t rows,
+                                       int64_t feat, int64_t batches, void* stream)
+{
+    if (out == nullptr || ptr == nullptr || rows < 0 || feat < 0 || batches < 0 || !IsIndexType(ptr_type)) {
+        return OPSGNN_ERR_INVALID;
+    }
+    cudaStream_t s = AsStream(stream);
+    switch (out_type) {
+        case OPSGNN_I8:
+            return IntegerMean<int8_t>(out, ptr, ptr_type, rows, feat, batches, s);
+        case OPSGNN_U8:
+            return IntegerMean<uint8_t>(out, ptr, ptr_type, rows, feat, batches, s);
+        case OPSGNN_I16:
+            return IntegerMean<int16_t>(out, ptr, ptr_type, rows, feat, batches, s);
+        case OPSGNN_I32:
+            return IntegerMean<int32_t>(out, ptr, ptr_type, rows, feat, batches, s);
+        case OPSGNN_I64:
+            return IntegerMean<int64_t>(out, ptr, ptr_type, rows, feat, batches, s);
+        default:
+            return OPSGNN_ERR_UNSUPPORTED;
+    }
+}
+
+extern "C" const char* opsgnn_status_string(int status)
+{
+    switch (status) {
+        case OPSGNN_OK:
+            return "ok";
+        case OPSGNN_ERR_INVALID:
+            return "invalid argument";
+        case OPSGNN_ERR_UNSUPPORTED:
+            return "unsupported dtype or mode";
+        case OPSGNN_ERR_WORKSPACE:
+            return "workspace too small or misaligned";
+        case OPSGNN_ERR_LIMIT:
+            return "size beyond a fixed maximum";
+        default:
+            return status > 0 ? cudaGetErrorString(static_cast<cudaError_t>(status)) : "unknown status";
+    }
+}
+
+extern "C" int opsgnn_sm_count(int* count)
+{
+    if (count == nullptr) {
+        return OPSGNN_ERR_INVALID;
+    }
+    *count = SmCount();
+    return OPSGNN_OK;
+}

@@ -1,0 +1,660 @@
+// CSR reduce engine for sm_100a.
+//
+//   out[b, r, k] = reduce_{e in [ptr[r], ptr[r+1])}  w(e, k) * mat[b, col(e), k]
+//
+// One kernel family serves weighted/unweighted SpMM (col = column indices), segment_csr / segment_coo
+// (col(e) = e) and segment log-sum-exp.  Design, in the order the data flows:
+//
+//  * Work is the merged list of "edges" and "row ends" (merge-path).  Every thread block owns kItemsPerCta
+//    consecutive items of that list and every warp kItemsPerWarp of them, so a power-law row with millions of
+//    edges is spread over many blocks and a run of empty rows costs the same as a run of edges.  The block's
+//    start row comes from a plan (one binary search per block, built once per graph by PlanKernel).
+//  * The block stages its row ends, column offsets and scalar weights in shared memory with plain coalesced
+//    loads; each warp then walks its items with warp-uniform control flow: all 32 lanes work on the same edge and
+//    own different features, so a gathered dense row is read with one or two 16-byte loads per lane (a 512-byte
+//    or 1-KiB fully coalesced request per warp) and kEdgeBatch rows are in flight per warp before the first use.
+//  * A row that ends inside the warp's items is written with streaming 16-byte stores.  Edges of a row whose end
+//    lies in a later warp are a "carry": carries are combined in item order after a block barrier, rows that
+//    end in the same block are patched in place, and at most one carry per block goes to global scratch where
+//    FixupKernel adds it to the row in block order.  No atomics: results are bitwise reproducible.
+//
+// Algorithmic bytes per launch (the roofline numerator): nnz*(sizeof(col)+sizeof(val)+K*sizeof(T)) +
+// rows*(sizeof(ptr)+K*sizeof(O)) (+ rows*K*8 for arg).
+#pragma once
+
+#include "common.cuh"
+
+namespace opsgnn {
+namespace csr {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kItemsPerWarp = 64;
+constexpr int kItemsPerCta = kWarps * kItemsPerWarp;
+
+enum ReduceKind { kSum = 0, kExtremum = 1, kLogSumExp = 2 };
+
+struct Identity {};  // col(e) = e
+
+struct Params {
+    const void* ptr;
+    const void* col;
+    const void* val;
+    const void* mat;
+    void* out;
+    int64_t* arg;
+    const int64_t* plan;  // start row of every block, num_cta + 1 entries
+    void* carry_val;      // [num_cta][carry_stride] accumulators
+    int64_t* carry_arg;   // [num_cta][carry_stride] (extrema only)
+    int64_t* carry_row;   // [num_cta] row that receives the block's carry, -1 for none
+    int64_t rows;
+    int64_t src_rows;
+    int64_t feat;
+    int64_t nnz;
+    int64_t batches;
+    int64_t arg_none;
+    int64_t num_cta;
+    int64_t carry_stride;  // gridDim.y * TILE
+    int tiles_per_batch;
+    int mean;      // kSum: divide by the row's edge count
+    int is_min;    // kExtremum
+    int extremum;  // OPSGNN_EXTREMUM_*
+    int has_val;
+    int wide;      // one weight per (edge, feature)
+};
+
+__host__ __device__ inline int64_t NumCta(int64_t rows, int64_t nnz) { return (rows + nnz + kItemsPerCta - 1) / kItemsPerCta; }
+
+// ---- plan: start row of each block's diagonal ----------------------------------------------------------------
+template <class PtrT>
+__global__ void PlanKernel(const PtrT* __restrict__ ptr, int64_t rows, int64_t nnz, int64_t num_cta,
+                           int64_t* __restrict__ plan)
+{
+    const int64_t b = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (b > num_cta) {
+        return;
+    }
+    const int64_t total = rows + nnz;
+    int64_t diag = b * kItemsPerCta;
+    diag = diag < total ? diag : total;
+    int64_t lo = diag > nnz ? diag - nnz : 0;
+    int64_t hi = diag < rows ? diag : rows;
+    while (lo < hi) {
+        const int64_t mid = (lo + hi) >> 1;
+        if (static_cast<int64_t>(ptr[mid + 1]) <= diag - 1 - mid) {
+            lo = mid + 1;
+        } else {
+            hi = mid;
+        }
+    }
+    plan[b] = lo;
+}
+
+// ---- element algebra -----------------------------------------------------------------------------------------
+template <class A> __device__ __forceinline__ bool IsNan(A v) { return v != v; }
+
+// Extremum update; `arg < 0` means nothing selected yet.  Earlier items are offered first, so strict compares
+// keep the first occurrence among ties.
+template <class A>
+__device__ __forceinline__ void ExtremumOffer(A& acc, int64_t& arg, A v, int64_t where, int is_min, int rule)
+{
+    const bool better = is_min ? (v < acc) : (v > acc);
+    bool take;
+    if (rule == OPSGNN_EXTREMUM_IGNORE_NAN) {
+        take = !IsNan(v) && (arg < 0 || better);
+    } else if (rule == OPSGNN_EXTREMUM_PROPAGATE_NAN) {
+        take = arg < 0 || better || (IsNan(v) && !IsNan(acc));
+    } else {
+        take = better;
+    }
+    if (take) {
+        acc = v;
+        arg = where;
+    }
+}
+
+// Seed of the "seeded" rule: the finite extreme of the storage dtype T, held in the accumulator type.
+template <class A, class T> __device__ __forceinline__ A ExtremumSeed(int is_min, int rule)
+{
+    if (rule == OPSGNN_EXTREMUM_SEEDED) {
+        return is_min ? static_cast<A>(Limits<T>::Max()) : static_cast<A>(Limits<T>::Lowest());
+    }
+    return A(0);
+}
+
+// log(exp(a) + exp(b)) with the conventions of torch.logsumexp: -inf is the empty sum, +inf absorbs, NaN spreads.
+__device__ __forceinline__ float LogAddExp(float a, float b)
+{
+    const float hi = fmaxf(a, b);  // fmaxf drops a NaN operand, so NaN is re-injected below
+    const float lo = fminf(a, b);
+    if (IsNan(a) || IsNan(b)) {
+        return a + b;
+    }
+    if (hi == lo) {  // covers (+inf,+inf) and (-inf,-inf) without inf-inf
+        return isinf(hi) ? hi : hi + 0.6931471805599453f;
+    }
+    return hi + log1pf(__expf(lo - hi));
+}
+
+// Online log-sum-exp state (running maximum m, sum of exp(x - m)).
+__device__ __forceinline__ void LseOffer(float& m, float& s, float x)
+{
+    if (x > m) {
+        s = s * __expf(m - x) + 1.0f;  // m = -inf initially: s = 0 * 0 + 1
+        m = x;
+    } else {
+        const float d = (x == m) ? 0.0f : x - m;  // equal infinities contribute exp(0)
+        s += __expf(d);                            // NaN input: d = NaN, s = NaN
+    }
+}
+
+__device__ __forceinline__ float LseFinish(float m, float s)
+{
+    if (s == 0.0f) {
+        return m;  // empty: m = -inf
+    }
+    return m + __logf(s);
+}
+
+template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK> struct Traits {
+    using A = typename AccOf<T>::type;
+    static constexpr int kTile = 32 * VEC * NV;
+    static constexpr int kElems = VEC * NV;
+    static constexpr int kEdgeBatch = (RK == kSum) ? (NV * VEC * sizeof(T) >= 32 ? 8 : 8) : 4;
+};
+
+// ---- main kernel ---------------------------------------------------------------------------------------------
+template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK>
+__global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
+{
+    using TR = Traits<T, O, PtrT, ColT, VEC, NV, RK>;
+    using A = typename TR::A;
+    constexpr int TILE = TR::kTile;
+    constexpr int ELEMS = TR::kElems;
+    constexpr int EB = TR::kEdgeBatch;
+    constexpr bool kIdentity = std::is_same<ColT, Identity>::value;
+    constexpr bool kHasArg = RK == kExtremum;
+
+    __shared__ int s_end[kItemsPerCta + 1];
+    __shared__ int64_t s_off[kItemsPerCta];  // col(e) * K
+    __shared__ T s_val[kItemsPerCta];
+    __shared__ int s_split[kWarps + 1];
+    __shared__ int s_carry_row[kWarps];
+    __shared__ A s_carry[kWarps][TILE];
+    __shared__ int64_t s_carry_arg[kHasArg ? kWarps : 1][kHasArg ? TILE : 1];
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int64_t cta = blockIdx.x;
+    const int batch = blockIdx.y / p.tiles_per_batch;
+    const int tile = blockIdx.y - batch * p.tiles_per_batch;
+    const int64_t kbase = static_cast<int64_t>(tile) * TILE;
+    const int64_t K = p.feat;
+
+    const PtrT* __restrict__ ptr = static_cast<const PtrT*>(p.ptr);
+    const T* __restrict__ mat = static_cast<const T*>(p.mat) + static_cast<int64_t>(batch) * p.src_rows * K;
+    const T* __restrict__ val = static_cast<const T*>(p.val);
+    O* __restrict__ out = static_cast<O*>(p.out) + static_cast<int64_t>(batch) * p.rows * K;
+    int64_t* __restrict__ arg = kHasArg ? p.arg + static_cast<int64_t>(batch) * p.rows * K : nullptr;
+
+    // ---- stage this block's items --------------------------------------------------------------------------
+    const int64_t total = p.rows + p.nnz;
+    const int64_t d0 = cta * kItemsPerCta;
+    const int64_t d1 = (d0 + kItemsPerCta < total) ? d0 + kItemsPerCta : total;
+    const int64_t row0 = p.plan[cta];
+    const int64_t row1 = p.plan[cta + 1];
+    const int64_t e0 = d0 - row0;
+    int nR = static_cast<int>(row1 - row0);
+    int nE = static_cast<int>((d1 - row1) - e0);
+    // A malformed plan or pointer array must not index outside the staging buffers.
+    nR = nR < 0 ? 0 : (nR > kItemsPerCta ? kItemsPerCta : nR);
+    nE = nE < 0 ? 0 : (nE > kItemsPerCta ? kItemsPerCta : nE);
+
+    for (int i = tid; i < nR; i += kThreads) {
+        int64_t rel = static_cast<int64_t>(LoadStream(ptr + row0 + 1 + i)) - e0;
+        rel = rel < 0 ? 0 : (rel > nE ? nE : rel);
+        s_end[i] = static_cast<int>(rel);
+    }
+    if (tid == 0) {
+        s_end[nR] = 0x7fffffff;
+    }
+    for (int j = tid; j < nE; j += kThreads) {
+        int64_t c;
+        if constexpr (kIdentity) {
+            c = e0 + j;
+        } else {
+            c = static_cast<int64_t>(LoadStream(static_cast<const ColT*>(p.col) + e0 + j));
+        }
+        c = c < 0 ? 0 : (c >= p.src_rows ? p.src_rows - 1 : c);  // validated upstream; never fault on a bad index
+        s_off[j] = c * K;
+        if (p.has_val && !p.wide) {
+            s_val[j] = LoadStream(val + e0 + j);
+        }
+    }
+    __syncthreads();
+    if (tid <= kWarps) {
+        int diag = tid * kItemsPerWarp;
+        diag = diag < nR + nE ? diag : nR + nE;
+        int lo = diag > nE ? diag - nE : 0;
+        int hi = diag < nR ? diag : nR;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (s_end[mid] <= diag - 1 - mid) {
+                lo = mid + 1;
+            } else {
+                hi = mid;
+            }
+        }
+        s_split[tid] = lo;
+    }
+    __syncthreads();
+
+    // ---- per-warp walk ---------------------------------------------------------------------------------------
+    int dw0 = warp * kItemsPerWarp;
+    int dw1 = dw0 + kItemsPerWarp;
+    dw0 = dw0 < nR + nE ? dw0 : nR + nE;
+    dw1 = dw1 < nR + nE ? dw1 : nR + nE;
+    int i = s_split[warp];
+    const int i1 = s_split[warp + 1];
+    int j = dw0 - i;
+    const int j1 = dw1 - i1;
+
+    // feature offsets owned by this lane: vector v covers [koff[v], koff[v] + VEC)
+    bool live[NV];
+    int64_t koff[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        koff[v] = kbase + static_cast<int64_t>(v * 32 + lane) * VEC;
+        live[v] = koff[v] < K;
+    }
+
+    A acc[ELEMS];
+    A aux[RK == kLogSumExp ? ELEMS : 1];       // sum of exponentials
+    int64_t where[kHasArg ? ELEMS : 1];        // selected edge, -1 for none
+    const A seed = (RK == kExtremum) ? ExtremumSeed<A, T>(p.is_min, p.extremum) : A(0);
+    auto reset = [&]() {
+#pragma unroll
+        for (int q = 0; q < ELEMS; ++q) {
+            if constexpr (RK == kLogSumExp) {
+                acc[q] = -INFINITY;
+                aux[q] = 0;
+            } else {
+                acc[q] = seed;
+            }
+            if constexpr (kHasArg) {
+                where[q] = -1;
+            }
+        }
+    };
+    reset();
+    bool dirty = false;
+
+    auto flush = [&](int local_row) {
+        const int64_t row = row0 + local_row;
+        A scale = A(1);
+        bool divide = false;
+        if constexpr (RK == kSum) {
+            if (p.mean) {
+                const int64_t degree = static_cast<int64_t>(ptr[row + 1]) - static_cast<int64_t>(ptr[row]);
+                if (degree > 0) {
+                    scale = static_cast<A>(degree);
+                    divide = true;
+                }
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            if (!live[v]) {
+                continue;
+            }
+            Pack<O, VEC> packed;
+            Pack<int64_t, VEC> packed_arg;
+#pragma unroll
+            for (int c = 0; c < VEC; ++c) {
+                A value = acc[v * VEC + c];
+                if constexpr (RK == kSum) {
+                    if (divide) {
+                        value = value / scale;
+                    }
+                } else if constexpr (RK == kLogSumExp) {
+                    value = LseFinish(value, aux[v * VEC + c]);
+                } else {
+                    const int64_t w = where[v * VEC + c];
+                    if (w < 0) {
+                        value = A(0);
+                    }
+                    packed_arg.v[c] = w < 0 ? p.arg_none : w;
+                }
+                packed.v[c] = Narrow<O, A>(value);
+            }
+            const int64_t at = row * K + koff[v];
+            if constexpr (sizeof(O) * VEC == 32) {
+                StoreStream<O, VEC / 2>(out + at, *reinterpret_cast<Pack<O, VEC / 2>*>(&packed.v[0]));
+                StoreStream<O, VEC / 2>(out + at + VEC / 2, *reinterpret_cast<Pack<O, VEC / 2>*>(&packed.v[VEC / 2]));
+            } else {
+                StoreStream<O, VEC>(out + at, packed);
+            }
+            if constexpr (kHasArg) {
+#pragma unroll
+                for (int c = 0; c < VEC; c += 2) {
+                    if constexpr (VEC >= 2) {
+                        StoreStream<int64_t, 2>(arg + at + c, *reinterpret_cast<Pack<int64_t, 2>*>(&packed_arg.v[c]));
+                    } else {
+                        arg[at] = packed_arg.v[0];
+                    }
+                }
+            }
+        }
+    };
+
+    int next_end = s_end[i];
+    while (j < j1) {
+        const int nb = (j1 - j < EB) ? j1 - j : EB;
+        Pack<T, VEC> x[EB][NV];
+#pragma unroll
+        for (int t = 0; t < EB; ++t) {
+            if (t < nb) {
+                const T* rowp = mat + s_off[j + t];
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    if (live[v]) {
+                        x[t][v] = LoadGather<T, VEC>(rowp + koff[v]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < EB; ++t) {
+            if (t < nb) {
+                const int e = j + t;
+                while (next_end <= e) {
+                    flush(i);
+                    reset();
+                    dirty = false;
+                    ++i;
+                    next_end = s_end[i];
+                }
+                A w = A(1);
+                if (p.has_val && !p.wide) {
+                    w = Widen<A, T>(s_val[e]);
+                }
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    if (!live[v]) {
+                        continue;
+                    }
+                    Pack<T, VEC> wv;
+                    if (p.wide) {
+                        wv = LoadGather<T, VEC>(val + (e0 + e) * K + koff[v]);
+                    }
+#pragma unroll
+                    for (int c = 0; c < VEC; ++c) {
+                        const int q = v * VEC + c;
+                        A value = Widen<A, T>(x[t][v].v[c]);
+                        if (p.wide) {
+                            w = Widen<A, T>(wv.v[c]);
+                        }
+                        if constexpr (RK == kSum) {
+                            acc[q] += w * value;
+                        } else if constexpr (RK == kExtremum) {
+                            if (p.has_val) {
+                                value = value * w;
+                            }
+                            ExtremumOffer<A>(acc[q], where[q], value, e0 + e, p.is_min, p.extremum);
+                        } else {
+                            LseOffer(acc[q], aux[q], value);
+                        }
+                    }
+                }
+                dirty = true;
+            }
+        }
+        j += nb;
+    }
+    while (i < i1) {
+        flush(i);
+        reset();
+        dirty = false;
+        ++i;
+    }
+
+    // ---- carries -------------------------------------------------------------------------------------------------
+    if (lane == 0) {
+        s_carry_row[warp] = dirty ? i1 : -1;
+    }
+    if (dirty) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+#pragma unroll
+            for (int c = 0; c < VEC; ++c) {
+                const int q = v * VEC + c;
+                const int f = (v * 32 + lane) * VEC + c;
+                if constexpr (RK == kLogSumExp) {
+                    s_carry[warp][f] = LseFinish(acc[q], aux[q]);
+                } else {
+                    s_carry[warp][f] = acc[q];
+                }
+                if constexpr (kHasArg) {
+                    s_carry_arg[warp][f] = where[q];
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    bool any = false;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+        any |= s_carry_row[w] >= 0;
+    }
+    if (tid == 0 && blockIdx.y == 0) {
+        bool leaves = false;  // a carry whose row ends in a later block
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            leaves |= s_carry_row[w] >= nR && s_carry_row[w] >= 0;
+        }
+        p.carry_row[cta] = leaves ? row0 + nR : -1;
+    }
+    if (!any) {
+        return;
+    }
+    A* __restrict__ carry_val = static_cast<A*>(p.carry_val) + cta * p.carry_stride + static_cast<int64_t>(blockIdx.y) * TILE;
+    int64_t* __restrict__ carry_arg =
+        kHasArg ? p.carry_arg + cta * p.carry_stride + static_cast<int64_t>(blockIdx.y) * TILE : nullptr;
+
+    for (int f = tid; f < TILE; f += kThreads) {
+        const int64_t k = kbase + f;
+        if (k >= K) {
+            continue;
+        }
+        int run_row = -1;
+        A run_acc = A(0);
+        int64_t run_arg = -1;
+        auto apply = [&]() {
+            if (run_row < 0) {
+                return;
+            }
+            if (run_row >= nR) {  // the row ends in a later block
+                carry_val[f] = run_acc;
+                if constexpr (kHasArg) {
+                    carry_arg[f] = run_arg;
+                }
+                return;
+            }
+            const int64_t row = row0 + run_row;
+            const int64_t at = row * K + k;
+            if constexpr (RK == kSum) {
+                A add = run_acc;
+                if (p.mean) {
+                    const int64_t degree = static_cast<int64_t>(ptr[row + 1]) - static_cast<int64_t>(ptr[row]);
+                    if (degree > 0) {
+                        add = add / static_cast<A>(degree);
+                    }
+                }
+                out[at] = Narrow<O, A>(add + Widen<A, O>(out[at]));
+            } else if constexpr (RK == kLogSumExp) {
+                out[at] = Narrow<O, A>(LogAddExp(run_acc, Widen<A, O>(out[at])));
+            } else {
+                const int64_t tail_arg = arg[at];
+                if (tail_arg != p.arg_none || run_arg >= 0) {
+                    A best = run_acc;
+                    int64_t best_arg = run_arg;
+                    if (tail_arg != p.arg_none) {
+                        ExtremumOffer<A>(best, best_arg, Widen<A, O>(out[at]), tail_arg, p.is_min, p.extremum);
+                    }
+                    if (best_arg >= 0) {
+                        out[at] = Narrow<O, A>(best);
+                        arg[at] = best_arg;
+                    }
+                }
+            }
+        };
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+            const int r = s_carry_row[w];
+            if (r < 0) {
+                continue;
+            }
+            const A value = s_carry[w][f];
+            if (r != run_row) {
+                apply();
+                run_row = r;
+                run_acc = value;
+                if constexpr (kHasArg) {
+                    run_arg = s_carry_arg[w][f];
+                }
+            } else if constexpr (RK == kSum) {
+                run_acc += value;
+            } else if constexpr (RK == kLogSumExp) {
+                run_acc = LogAddExp(run_acc, value);
+            } else {
+                const int64_t a = s_carry_arg[w][f];
+                if (a >= 0) {
+                    ExtremumOffer<A>(run_acc, run_arg, value, a, p.is_min, p.extremum);
+                }
+            }
+        }
+        apply();
+    }
+}
+
+// ---- cross-block carries ---------------------------------------------------------------------------------------
+// One warp per block index: the first block of a run of equal carry rows sums the run in block order and patches
+// the row, so the result does not depend on scheduling.
+template <class T, class O, class PtrT, int RK>
+__global__ void __launch_bounds__(kThreads) FixupKernel(const Params p)
+{
+    using A = typename AccOf<T>::type;
+    constexpr bool kHasArg = RK == kExtremum;
+    const int lane = threadIdx.x & 31;
+    const int64_t b = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+    if (b >= p.num_cta) {
+        return;
+    }
+    const int64_t row = p.carry_row[b];
+    if (row < 0 || row >= p.rows || (b > 0 && p.carry_row[b - 1] == row)) {
+        return;
+    }
+    const PtrT* __restrict__ ptr = static_cast<const PtrT*>(p.ptr);
+    const A* __restrict__ carry_val = static_cast<const A*>(p.carry_val);
+    const int64_t K = p.feat;
+    const int64_t tile = p.carry_stride / (p.tiles_per_batch * p.batches);
+    A scale = A(1);
+    bool divide = false;
+    if (RK == kSum && p.mean) {
+        const int64_t degree = static_cast<int64_t>(ptr[row + 1]) - static_cast<int64_t>(ptr[row]);
+        if (degree > 0) {
+            scale = static_cast<A>(degree);
+            divide = true;
+        }
+    }
+    const int64_t width = p.batches * K;
+    for (int64_t x = lane; x < width; x += 32) {
+        const int64_t batch = x / K;
+        const int64_t k = x - batch * K;
+        // position of feature k of this batch inside a carry row: tiles are padded to `tile` features
+        const int64_t f = (batch * p.tiles_per_batch + k / tile) * tile + k % tile;
+        A run_acc = carry_val[b * p.carry_stride + f];
+        int64_t run_arg = kHasArg ? p.carry_arg[b * p.carry_stride + f] : 0;
+        for (int64_t n = b + 1; n < p.num_cta && p.carry_row[n] == row; ++n) {
+            const A value = carry_val[n * p.carry_stride + f];
+            if constexpr (RK == kSum) {
+                run_acc += value;
+            } else if constexpr (RK == kLogSumExp) {
+                run_acc = LogAddExp(run_acc, value);
+            } else {
+                const int64_t a = p.carry_arg[n * p.carry_stride + f];
+                if (a >= 0) {
+                    ExtremumOffer<A>(run_acc, run_arg, value, a, p.is_min, p.extremum);
+                }
+            }
+        }
+        O* out = static_cast<O*>(p.out);
+        const int64_t at = (batch * p.rows + row) * K + k;
+        if constexpr (RK == kSum) {
+            if (divide) {
+                run_acc = run_acc / scale;
+            }
+            out[at] = Narrow<O, A>(run_acc + Widen<A, O>(out[at]));
+        } else if constexpr (RK == kLogSumExp) {
+            out[at] = Narrow<O, A>(LogAddExp(run_acc, Widen<A, O>(out[at])));
+        } else {
+            const int64_t tail_arg = p.arg[at];
+            if (tail_arg != p.arg_none) {
+                ExtremumOffer<A>(run_acc, run_arg, Widen<A, O>(out[at]), tail_arg, p.is_min, p.extremum);
+            }
+            if (run_arg >= 0) {
+                out[at] = Narrow<O, A>(run_acc);
+                p.arg[at] = run_arg;
+            }
+        }
+    }
+}
+
+// ---- host-side launch ----------------------------------------------------------------------------------------
+template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK>
+int Launch(Params p, cudaStream_t stream)
+{
+    constexpr int TILE = 32 * VEC * NV;
+    p.tiles_per_batch = static_cast<int>(CeilDiv(p.feat, TILE));
+    const int64_t grid_y = p.tiles_per_batch * p.batches;
+    if (grid_y > 65535 || p.num_cta > 2147483647LL) {
+        return OPSGNN_ERR_LIMIT;
+    }
+    p.carry_stride = grid_y * TILE;
+    const dim3 grid(static_cast<unsigned>(p.num_cta), static_cast<unsigned>(grid_y));
+    ReduceKernel<T, O, PtrT, ColT, VEC, NV, RK><<<grid, kThreads, 0, stream>>>(p);
+    int status = LaunchStatus();
+    if (status != OPSGNN_OK) {
+        return status;
+    }
+    const unsigned fix_grid = static_cast<unsigned>(CeilDiv(p.num_cta, kWarps));
+    FixupKernel<T, O, PtrT, RK><<<fix_grid, kThreads, 0, stream>>>(p);
+    return LaunchStatus();
+}
+
+// Picks the lane layout: 16-byte vectors when the feature width and base addresses allow it.
+template <class T, class O, class PtrT, class ColT, int RK>
+int LaunchShaped(const Params& p, cudaStream_t stream)
+{
+    constexpr int kVec = 16 / sizeof(T);
+    const bool vector_ok = sizeof(T) <= 4 && sizeof(T) >= 2 && p.feat % kVec == 0 && Aligned(p.mat, 16) && Aligned(p.out, 16) &&
+                           (!p.wide || Aligned(p.val, 16)) && (RK != kExtremum || Aligned(p.arg, 16));
+    if constexpr (sizeof(T) == 4) {
+        if (vector_ok && p.feat > 128) {
+            return Launch<T, O, PtrT, ColT, 4, 2, RK>(p, stream);
+        }
+        if (vector_ok) {
+            return Launch<T, O, PtrT, ColT, 4, 1, RK>(p, stream);
+        }
+    } else if constexpr (sizeof(T) == 2) {
+        if (vector_ok) {
+            return Launch<T, O, PtrT, ColT, 8, 1, RK>(p, stream);
+        }
+    }
+    return Launch<T, O, PtrT, ColT, 1, 4, RK>(p, stream);
+}
+
+}  // namespace csr
+}  // namespace opsgnn
