@@ -89,7 +89,9 @@ typedef struct OpsgnnCsrReduceDesc {
     int64_t feat;        /* K: features per row                                    */
     int64_t nnz;         /* E: edges; with col == NULL must equal src_rows or less */
     int64_t batches;     /* B: leading batch count of mat/out (>= 1)               */
-    int64_t value_width; /* 0 (val NULL), 1 (one weight per edge) or K             */
+    int64_t value_width; /* 0 (val NULL), 1 (one weight per edge), K, or a divisor */
+                         /* W of K: val is [E, W] and feature k uses val[e, k/(K/W)] */
+                         /* (one attention weight per head)                        */
     int64_t arg_none;    /* arg written where no element was selected              */
     int32_t reduce;      /* OPSGNN_REDUCE_*                                        */
     int32_t extremum;    /* OPSGNN_EXTREMUM_* (min/max only)                       */
@@ -175,8 +177,10 @@ OPSGNN_API int opsgnn_spmm_value_grad(const int64_t* ptr, const int64_t* col, co
 OPSGNN_API int opsgnn_ind2ptr(const int64_t* ind, int64_t nnz, int64_t* ptr, int64_t rows, void* stream);
 /* ind[e] = row r with ptr[r] <= e < ptr[r+1].  Replaces Ptr2Ind (csrc/npu/ptr2ind/op_kernel/arch35/ptr2ind.cpp:20-52). */
 OPSGNN_API int opsgnn_ptr2ind(const int64_t* ptr, int64_t rows, int64_t* ind, int64_t nnz, void* stream);
-/* status[0] = 0 valid, 1 bad pointer array, 2 column out of range (maximum over the structure).
- * Replaces TorchSparseSpmmValidate (torch_sparse_spmm_kernel.h:399-430).  index_type selects int32/int64. */
+/* status[0] = OR of: 1 ptr[0] != 0 or ptr[rows] != nnz, 2 pointer outside [0, nnz], 4 decreasing pointer,
+ * 8 column outside [0, cols) (col may be NULL to skip the column check); 0 means a valid structure.
+ * Replaces TorchSparseSpmmValidate (torch_sparse_spmm_kernel.h:399-430) and the device half of the CSR proof of
+ * csrc/npu/common/spmm/host_proof_cache.h:243-310.  index_type selects int32/int64. */
 OPSGNN_API int opsgnn_csr_validate(const void* ptr, const void* col, int index_type, int64_t rows, int64_t cols, int64_t nnz,
                         int32_t* status, void* stream);
 /* out[i, :] = value[perm[i], :].  Replaces TorchSparseSpmmPermuteValues (torch_sparse_spmm.cpp:16-36). */

@@ -45,7 +45,7 @@ int CheckDesc(const OpsgnnCsrReduceDesc* d)
     if (KindOf(d->reduce) < 0 || !IsIndexType(d->ptr_type)) {
         return OPSGNN_ERR_INVALID;
     }
-    if (d->value_width != 0 && d->value_width != 1 && d->value_width != d->feat) {
+    if (d->value_width < 0 || (d->value_width > 1 && (d->feat == 0 || d->feat % d->value_width != 0))) {
         return OPSGNN_ERR_INVALID;
     }
     if (d->nnz > 0 && d->src_rows == 0) {
@@ -161,7 +161,9 @@ extern "C" int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* pt
     p.is_min = d.reduce == OPSGNN_REDUCE_MIN;
     p.extremum = d.extremum;
     p.has_val = val != nullptr;
-    p.wide = val != nullptr && d.value_width == d.feat && d.feat != 1;
+    p.wide = (val == nullptr || d.value_width == 1) ? 0 : (d.value_width == d.feat ? 1 : 2);
+    p.val_width = d.value_width;
+    p.val_group = d.value_width > 0 ? d.feat / d.value_width : 1;
     char* cursor = static_cast<char*>(workspace);
     const int64_t width = CarryWidth(d);
     p.carry_row = reinterpret_cast<int64_t*>(cursor);

@@ -60,10 +60,19 @@ struct Params {
     int is_min;    // kExtremum
     int extremum;  // OPSGNN_EXTREMUM_*
     int has_val;
-    int wide;      // one weight per (edge, feature)
+    int wide;      // 0: one weight per edge (or none); 1: one per (edge, feature); 2: one per (edge, feature group)
+    int64_t val_width;  // weights per edge
+    int64_t val_group;  // wide == 2: consecutive features that share a weight (feat / val_width)
 };
 
 __host__ __device__ inline int64_t NumCta(int64_t rows, int64_t nnz) { return (rows + nnz + kItemsPerCta - 1) / kItemsPerCta; }
+
+// Edges actually covered by the pointer array, given the host's upper bound (the grid is sized for the bound).
+__host__ __device__ inline int64_t ActualEdges(int64_t first, int64_t last, int64_t bound)
+{
+    const int64_t span = last - first;
+    return span < 0 ? 0 : (span > bound ? bound : span);
+}
 
 // ---- plan: start row of each block's diagonal ----------------------------------------------------------------
 template <class PtrT>
@@ -74,6 +83,9 @@ __global__ void PlanKernel(const PtrT* __restrict__ ptr, int64_t rows, int64_t n
     if (b > num_cta) {
         return;
     }
+    // Edges are counted from ptr[0]: segment pointers need not start at zero nor cover every source row.
+    const int64_t base = static_cast<int64_t>(ptr[0]);
+    nnz = ActualEdges(base, static_cast<int64_t>(ptr[rows]), nnz);
     const int64_t total = rows + nnz;
     int64_t diag = b * kItemsPerCta;
     diag = diag < total ? diag : total;
@@ -81,7 +93,7 @@ __global__ void PlanKernel(const PtrT* __restrict__ ptr, int64_t rows, int64_t n
     int64_t hi = diag < rows ? diag : rows;
     while (lo < hi) {
         const int64_t mid = (lo + hi) >> 1;
-        if (static_cast<int64_t>(ptr[mid + 1]) <= diag - 1 - mid) {
+        if (static_cast<int64_t>(ptr[mid + 1]) - base <= diag - 1 - mid) {
             lo = mid + 1;
         } else {
             hi = mid;
@@ -199,12 +211,20 @@ __global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
     int64_t* __restrict__ arg = kHasArg ? p.arg + static_cast<int64_t>(batch) * p.rows * K : nullptr;
 
     // ---- stage this block's items --------------------------------------------------------------------------
-    const int64_t total = p.rows + p.nnz;
+    const int64_t base = static_cast<int64_t>(ptr[0]);
+    const int64_t total = p.rows + ActualEdges(base, static_cast<int64_t>(ptr[p.rows]), p.nnz);
     const int64_t d0 = cta * kItemsPerCta;
+    if (d0 >= total) {  // the grid is sized for the host's edge bound
+        if (tid == 0 && blockIdx.y == 0) {
+            p.carry_row[cta] = -1;
+        }
+        return;
+    }
     const int64_t d1 = (d0 + kItemsPerCta < total) ? d0 + kItemsPerCta : total;
     const int64_t row0 = p.plan[cta];
     const int64_t row1 = p.plan[cta + 1];
-    const int64_t e0 = d0 - row0;
+    const int64_t e0 = d0 - row0;  // first edge of the block, counted from `base`
+    const int64_t a0 = base + e0;  // the same edge as an absolute position in col / val / the source rows
     int nR = static_cast<int>(row1 - row0);
     int nE = static_cast<int>((d1 - row1) - e0);
     // A malformed plan or pointer array must not index outside the staging buffers.
@@ -212,7 +232,7 @@ __global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
     nE = nE < 0 ? 0 : (nE > kItemsPerCta ? kItemsPerCta : nE);
 
     for (int i = tid; i < nR; i += kThreads) {
-        int64_t rel = static_cast<int64_t>(LoadStream(ptr + row0 + 1 + i)) - e0;
+        int64_t rel = static_cast<int64_t>(LoadStream(ptr + row0 + 1 + i)) - a0;
         rel = rel < 0 ? 0 : (rel > nE ? nE : rel);
         s_end[i] = static_cast<int>(rel);
     }
@@ -222,14 +242,14 @@ __global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
     for (int j = tid; j < nE; j += kThreads) {
         int64_t c;
         if constexpr (kIdentity) {
-            c = e0 + j;
+            c = a0 + j;
         } else {
-            c = static_cast<int64_t>(LoadStream(static_cast<const ColT*>(p.col) + e0 + j));
+            c = static_cast<int64_t>(LoadStream(static_cast<const ColT*>(p.col) + a0 + j));
         }
         c = c < 0 ? 0 : (c >= p.src_rows ? p.src_rows - 1 : c);  // validated upstream; never fault on a bad index
         s_off[j] = c * K;
         if (p.has_val && !p.wide) {
-            s_val[j] = LoadStream(val + e0 + j);
+            s_val[j] = LoadStream(val + a0 + j);
         }
     }
     __syncthreads();
@@ -267,6 +287,12 @@ __global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
     for (int v = 0; v < NV; ++v) {
         koff[v] = kbase + static_cast<int64_t>(v * 32 + lane) * VEC;
         live[v] = koff[v] < K;
+    }
+
+    int64_t group_of[NV];  // wide == 2: weight slot of each owned vector
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        group_of[v] = p.wide == 2 ? koff[v] / p.val_group : 0;
     }
 
     A acc[ELEMS];
@@ -385,14 +411,16 @@ __global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
                         continue;
                     }
                     Pack<T, VEC> wv;
-                    if (p.wide) {
-                        wv = LoadGather<T, VEC>(val + (e0 + e) * K + koff[v]);
+                    if (p.wide == 1) {
+                        wv = LoadGather<T, VEC>(val + (a0 + e) * K + koff[v]);
+                    } else if (p.wide == 2) {
+                        w = Widen<A, T>(__ldg(val + (a0 + e) * p.val_width + group_of[v]));
                     }
 #pragma unroll
                     for (int c = 0; c < VEC; ++c) {
                         const int q = v * VEC + c;
                         A value = Widen<A, T>(x[t][v].v[c]);
-                        if (p.wide) {
+                        if (p.wide == 1) {
                             w = Widen<A, T>(wv.v[c]);
                         }
                         if constexpr (RK == kSum) {
@@ -401,7 +429,7 @@ __global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
                             if (p.has_val) {
                                 value = value * w;
                             }
-                            ExtremumOffer<A>(acc[q], where[q], value, e0 + e, p.is_min, p.extremum);
+                            ExtremumOffer<A>(acc[q], where[q], value, a0 + e, p.is_min, p.extremum);
                         } else {
                             LseOffer(acc[q], aux[q], value);
                         }
@@ -640,7 +668,8 @@ int LaunchShaped(const Params& p, cudaStream_t stream)
 {
     constexpr int kVec = 16 / sizeof(T);
     const bool vector_ok = sizeof(T) <= 4 && sizeof(T) >= 2 && p.feat % kVec == 0 && Aligned(p.mat, 16) && Aligned(p.out, 16) &&
-                           (!p.wide || Aligned(p.val, 16)) && (RK != kExtremum || Aligned(p.arg, 16));
+                           (p.wide != 1 || Aligned(p.val, 16)) && (p.wide != 2 || p.val_group % kVec == 0) &&
+                           (RK != kExtremum || Aligned(p.arg, 16));
     if constexpr (sizeof(T) == 4) {
         if (vector_ok && p.feat > 128) {
             return Launch<T, O, PtrT, ColT, 4, 2, RK>(p, stream);

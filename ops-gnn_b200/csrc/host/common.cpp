@@ -1,0 +1,172 @@
+#include "common.h"
+
+#include <c10/util/intrusive_ptr.h>
+
+#include <list>
+#include <mutex>
+
+namespace opsgnn {
+namespace {
+
+// Identity of a tensor's contents as far as torch can see them: the implementation object, its version counter and
+// the storage address.  Inference tensors have no version counter and are never cached.
+struct TensorKey {
+    const c10::TensorImpl* impl = nullptr;
+    const void* data = nullptr;
+    int64_t version = -1;
+    int64_t numel = 0;
+    std::optional<c10::weak_intrusive_ptr<c10::TensorImpl>> alive;
+
+    static std::optional<TensorKey> Of(const at::Tensor& t)
+    {
+        if (!t.defined() || t.is_inference()) {
+            return std::nullopt;
+        }
+        TensorKey key;
+        key.impl = t.unsafeGetTensorImpl();
+        key.data = t.const_data_ptr();
+        key.version = t._version();
+        key.numel = t.numel();
+        key.alive = c10::weak_intrusive_ptr<c10::TensorImpl>(t.getIntrusivePtr());
+        return key;
+    }
+
+    bool Matches(const TensorKey& other) const
+    {
+        return impl == other.impl && data == other.data && version == other.version && numel == other.numel &&
+               alive.has_value() && !alive->expired();
+    }
+};
+
+struct PlanEntry {
+    TensorKey ptr;
+    int64_t rows, nnz;
+    at::Tensor plan;
+};
+
+struct FactsEntry {
+    TensorKey ptr;
+    std::optional<TensorKey> col;
+    int64_t rows, cols, nnz;
+    int facts;
+};
+
+constexpr size_t kCacheEntries = 32;
+std::mutex g_mutex;
+std::list<PlanEntry> g_plans;
+std::list<FactsEntry> g_facts;
+
+}  // namespace
+
+at::Tensor CsrPlan(const at::Tensor& ptr, int64_t rows, int64_t nnz_bound)
+{
+    auto key = TensorKey::Of(ptr);
+    if (key) {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        for (auto it = g_plans.begin(); it != g_plans.end(); ++it) {
+            if (it->rows == rows && it->nnz == nnz_bound && it->ptr.Matches(*key)) {
+                g_plans.splice(g_plans.begin(), g_plans, it);
+                return g_plans.front().plan;
+            }
+        }
+    }
+    int64_t bytes = 0;
+    CheckStatus(opsgnn_csr_plan_bytes(rows, nnz_bound, &bytes), "csr_plan");
+    auto plan = at::empty({bytes / 8}, ptr.options().dtype(at::kLong));
+    CheckStatus(opsgnn_csr_plan_build(ptr.const_data_ptr(), DtypeId(ptr.scalar_type(), "csr_plan"), rows, nnz_bound,
+                                      plan.data_ptr(), CurrentStream(ptr)),
+                "csr_plan");
+    if (key) {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        g_plans.push_front(PlanEntry{*key, rows, nnz_bound, plan});
+        if (g_plans.size() > kCacheEntries) {
+            g_plans.pop_back();
+        }
+    }
+    return plan;
+}
+
+void ClearCsrPlanCache()
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    g_plans.clear();
+}
+
+int CsrFacts(const at::Tensor& ptr, const std::optional<at::Tensor>& col, int64_t rows, int64_t cols, int64_t nnz)
+{
+    auto ptr_key = TensorKey::Of(ptr);
+    std::optional<TensorKey> col_key;
+    bool cacheable = ptr_key.has_value();
+    if (col) {
+        col_key = TensorKey::Of(*col);
+        cacheable = cacheable && col_key.has_value();
+    }
+    if (cacheable) {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        for (auto it = g_facts.begin(); it != g_facts.end(); ++it) {
+            const bool same_col = col_key.has_value() == it->col.has_value() && (!col_key || it->col->Matches(*col_key));
+            if (it->rows == rows && it->cols == cols && it->nnz == nnz && same_col && it->ptr.Matches(*ptr_key)) {
+                g_facts.splice(g_facts.begin(), g_facts, it);
+                return g_facts.front().facts;
+            }
+        }
+    }
+    auto status = at::empty({1}, ptr.options().dtype(at::kInt));
+    CheckStatus(opsgnn_csr_validate(ptr.const_data_ptr(), col ? col->const_data_ptr() : nullptr,
+                                    DtypeId(ptr.scalar_type(), "csr_validate"), rows, cols, nnz,
+                                    status.data_ptr<int32_t>(), CurrentStream(ptr)),
+                "csr_validate");
+    const int facts = status.item<int32_t>();
+    if (cacheable) {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        g_facts.push_front(FactsEntry{*ptr_key, col_key, rows, cols, nnz, facts});
+        if (g_facts.size() > kCacheEntries) {
+            g_facts.pop_back();
+        }
+    }
+    return facts;
+}
+
+void ClearCsrFactsCache()
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    g_facts.clear();
+}
+
+void RunCsrReduce(CsrReduceCall& call, const char* api)
+{
+    if (call.rows == 0 || call.feat == 0 || call.batches == 0) {
+        return;
+    }
+    OpsgnnCsrReduceDesc desc{};
+    desc.rows = call.rows;
+    desc.src_rows = call.src_rows;
+    desc.feat = call.feat;
+    desc.nnz = call.nnz;
+    desc.batches = call.batches;
+    desc.value_width = call.val ? call.value_width : 0;
+    desc.arg_none = call.arg_none;
+    desc.reduce = call.reduce;
+    desc.extremum = call.extremum;
+    desc.ptr_type = DtypeId(call.ptr.scalar_type(), api);
+    desc.col_type = call.col ? DtypeId(call.col->scalar_type(), api) : desc.ptr_type;
+    desc.in_type = DtypeId(call.mat.scalar_type(), api);
+    desc.out_type = DtypeId(call.out.scalar_type(), api);
+
+    const bool extremum = call.reduce == OPSGNN_REDUCE_MIN || call.reduce == OPSGNN_REDUCE_MAX;
+    at::Tensor arg;
+    if (extremum) {
+        arg = call.arg ? *call.arg : at::empty(call.out.sizes(), call.out.options().dtype(at::kLong));
+    }
+    at::Tensor plan = CsrPlan(call.ptr, call.rows, call.nnz);
+    int64_t bytes = 0;
+    CheckStatus(opsgnn_csr_reduce_workspace_bytes(&desc, &bytes), api);
+    at::Tensor scratch = Scratch(bytes, call.out);
+    CheckStatus(opsgnn_csr_reduce(&desc, call.ptr.const_data_ptr(), call.col ? call.col->const_data_ptr() : nullptr,
+                                  call.val ? call.val->const_data_ptr() : nullptr, call.mat.const_data_ptr(),
+                                  call.out.data_ptr(), extremum ? arg.data_ptr<int64_t>() : nullptr,
+                                  plan.const_data_ptr(), scratch.data_ptr(), scratch.numel(), CurrentStream(call.out)),
+                api);
+}
+
+}  // namespace opsgnn

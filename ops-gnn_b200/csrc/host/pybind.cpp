@@ -1,0 +1,127 @@
+// Python binding of the launch planners.  Function names, argument names and defaults are those of the reference's
+// csrc/pybind.cpp:92-257 (both of its architecture branches, since one GPU build offers every operator); the module
+// attribute `npu_arch` is kept for callers that read it and names this build "sm_100a".
+#include <ATen/core/dispatch/Dispatcher.h>
+#include <c10/core/DispatchKey.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include "ops.h"
+
+namespace py = pybind11;
+
+namespace {
+
+bool HasKernelForKey(const std::string& op_name, c10::DispatchKey key)
+{
+    const auto op = c10::Dispatcher::singleton().findOp(c10::OperatorName(op_name, ""));
+    return op.has_value() && op->hasKernelForDispatchKey(key);
+}
+
+void BindSpmm(py::module_& m)
+{
+    using namespace opsgnn;
+    m.def("spmm_max_csr", &SpmmMaxCsr, py::arg("indptr"), py::arg("indices"), py::arg("x"), py::arg("out") = py::none(),
+          "CSR SpMM max on CUDA", py::call_guard<py::gil_scoped_release>());
+    m.def("spmm_min_csr", &SpmmMinCsr, py::arg("indptr"), py::arg("indices"), py::arg("x"), py::arg("out") = py::none(),
+          "CSR SpMM min on CUDA", py::call_guard<py::gil_scoped_release>());
+    m.def("spmm_sum_csr", &SpmmSumCsr, py::arg("indptr"), py::arg("indices"), py::arg("x"), py::arg("out") = py::none(),
+          "CSR SpMM sum on CUDA", py::call_guard<py::gil_scoped_release>());
+    m.def("unified_spmm_csr", &UnifiedSpmmCsr, py::arg("indptr"), py::arg("indices"), py::arg("x"),
+          py::arg("op") = "copy_lhs", py::arg("reduce") = "sum", py::arg("out") = py::none(),
+          "Unified two-dimensional CSR SpMM on CUDA", py::call_guard<py::gil_scoped_release>());
+    m.def("spmm_weighted_csr", &SpmmWeightedCsr, py::arg("indptr"), py::arg("indices"), py::arg("x"), py::arg("weight"),
+          py::arg("reduce") = "sum",
+          "CSR SpMM with one edge weight per feature group (fused `mul` message); not part of the reference binding",
+          py::call_guard<py::gil_scoped_release>());
+    auto sub = m.def_submodule("torch_sparse_spmm", "torch_sparse SpMM on CUDA");
+    sub.def("forward", &TorchSparseSpmmForward, py::arg("ptr"), py::arg("col"), py::arg("value"), py::arg("mat"),
+            py::arg("reduce"), py::arg("outtype"), py::call_guard<py::gil_scoped_release>());
+    sub.def("validate", &TorchSparseSpmmValidate, py::arg("ptr"), py::arg("col"), py::arg("n"),
+            py::call_guard<py::gil_scoped_release>());
+    sub.def("value_backward", &TorchSparseSpmmValueGrad, py::arg("ptr"), py::arg("col"), py::arg("mat"), py::arg("grad"),
+            py::arg("reduce"), py::arg("width"), py::call_guard<py::gil_scoped_release>());
+    sub.def("convert", &TorchSparseSpmmConvert, py::arg("src"), py::arg("output"), py::arg("to_ptr"),
+            py::call_guard<py::gil_scoped_release>());
+    sub.def("permute_values", &TorchSparseSpmmPermuteValues, py::arg("value"), py::arg("perm"),
+            py::call_guard<py::gil_scoped_release>());
+    sub.def("tensor_version", &TorchSparseSpmmTensorVersion, py::arg("tensor"));
+}
+
+void BindSegment(py::module_& m)
+{
+    using namespace opsgnn;
+    m.def("segment_csr", &segment_csr, py::arg("src"), py::arg("indptr"), py::arg("out") = py::none(),
+          py::arg("reduce") = "sum", py::arg("return_arg") = true, py::call_guard<py::gil_scoped_release>());
+    m.def(
+        "segment_csr_value",
+        [](at::Tensor src, at::Tensor indptr, std::optional<at::Tensor> out, const std::string& reduce) {
+            return segment_csr(std::move(src), std::move(indptr), std::move(out), reduce, false)[0];
+        },
+        py::arg("src"), py::arg("indptr"), py::arg("out") = py::none(), py::arg("reduce") = "sum",
+        py::call_guard<py::gil_scoped_release>());
+    m.attr("SEGMENT_COO_SUM") = static_cast<int32_t>(SEGMENT_COO_SUM);
+    m.attr("SEGMENT_COO_MEAN") = static_cast<int32_t>(SEGMENT_COO_MEAN);
+    m.attr("SEGMENT_COO_MIN") = static_cast<int32_t>(SEGMENT_COO_MIN);
+    m.attr("SEGMENT_COO_MAX") = static_cast<int32_t>(SEGMENT_COO_MAX);
+    m.def("segment_coo_forward", &segment_coo_forward, py::arg("src"), py::arg("index"), py::arg("out"),
+          py::arg("dim_size"), py::arg("reduce"), py::arg("return_arg") = true,
+          py::call_guard<py::gil_scoped_release>());
+    m.def(
+        "segment_coo_value",
+        [](at::Tensor src, at::Tensor index, std::optional<at::Tensor> out, std::optional<int64_t> dim_size,
+           int64_t reduce) {
+            return std::get<0>(segment_coo_forward(std::move(src), std::move(index), std::move(out), dim_size, reduce,
+                                                   false));
+        },
+        py::arg("src"), py::arg("index"), py::arg("out"), py::arg("dim_size"), py::arg("reduce"),
+        py::call_guard<py::gil_scoped_release>());
+    m.def("segment_logsumexp_forward", &segment_logsumexp_forward, py::arg("src"), py::arg("indptr"),
+          "CSR log-sum-exp forward on CUDA", py::call_guard<py::gil_scoped_release>());
+}
+
+void BindConvert(py::module_& m)
+{
+    using namespace opsgnn;
+    m.def("ind2ptr", &ind2ptr, py::arg("ind"), py::arg("M"),
+          "Convert sorted row indices to CSR row pointer, same as torch_sparse.ind2ptr",
+          py::call_guard<py::gil_scoped_release>());
+    m.def("ptr2ind", &ptr2ind, py::arg("ptr"), py::arg("E"),
+          "Convert CSR row pointer to row indices, same as torch_sparse.ptr2ind",
+          py::call_guard<py::gil_scoped_release>());
+    m.def("csr_facts", &csr_facts, py::arg("ptr"), py::arg("col"), py::arg("rows"), py::arg("cols"), py::arg("nnz"),
+          "Validation bit mask of a CSR structure: 1 end points, 2 pointer range, 4 decreasing pointer, 8 column range",
+          py::call_guard<py::gil_scoped_release>());
+    m.def("index_stats", &index_stats, py::arg("index"),
+          "int64[3] on the device: minimum, maximum and 1 when the index is non-decreasing",
+          py::call_guard<py::gil_scoped_release>());
+}
+
+}  // namespace
+
+void BindSddmm(py::module_& m);
+void BindScatter(py::module_& m);
+void BindGrouped(py::module_& m);
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
+{
+    m.doc() = "ops_gnn: CUDA (sm_100a) extension";
+    m.attr("npu_arch") = "sm_100a";
+    m.def(
+        "has_private_use1_kernel",
+        [](const std::string& op_name) { return HasKernelForKey(op_name, c10::DispatchKey::CUDA); },
+        py::arg("op_name"),
+        "True if the operator already has a kernel for this build's device key (CUDA), e.g. a pre-existing "
+        "third-party registration");
+    m.def("clear_native_caches", []() {
+        opsgnn::ClearCsrPlanCache();
+        opsgnn::ClearCsrFactsCache();
+    });
+    BindSegment(m);
+    BindSpmm(m);
+    BindConvert(m);
+    BindSddmm(m);
+    BindScatter(m);
+    BindGrouped(m);
+}

@@ -1,0 +1,59 @@
+"""ops_gnn for NVIDIA B200: sparse message-passing operators behind the ops-gnn Python API.
+
+The native extension is loaded from ``<package>/<target>/_pybind.so`` exactly as the reference does
+(python/ops_gnn/__init__.py:27-42 of ops-gnn); the single CUDA build exports the union of the operators the two
+Ascend builds expose for this path.  There is no CPU fallback: importing without the built extension fails.
+"""
+import importlib.util
+import os
+import sys
+
+import torch
+
+from ._device import select_target
+from .typing import OptTensor, Tensor
+
+__version__ = "0.1.0"
+
+try:
+    _target = select_target()
+    _library = os.path.join(os.path.dirname(__file__), _target, "_pybind.so")
+    _spec = importlib.util.spec_from_file_location(__name__ + "._pybind", _library)
+    _pybind = importlib.util.module_from_spec(_spec)
+    sys.modules[_spec.name] = _pybind
+    _spec.loader.exec_module(_pybind)
+except (ImportError, OSError, RuntimeError, ValueError, AttributeError) as exc:
+    raise ImportError(
+        "cannot import the ops_gnn._pybind native extension; the CUDA operators are unavailable. Check that "
+        "(1) `python ops-gnn_b200/build.py` has been run for this Python / PyTorch, "
+        "(2) libopsgnn_b200.so sits next to _pybind.so, and (3) the GPU is an sm_100a device. "
+        f"Original error: {exc}"
+    ) from exc
+
+from .ind2ptr import ind2ptr
+from .ptr2ind import ptr2ind
+from .segment_csr import (
+    segment_add_csr, segment_csr, segment_max_csr, segment_mean_csr, segment_min_csr, segment_sum_csr,
+)
+from .segment_reduce import segment_reduce
+from .segment_coo import (
+    segment_add_coo, segment_coo, segment_max_coo, segment_mean_coo, segment_min_coo, segment_sum_coo,
+)
+from .segment_logsumexp import segment_logsumexp
+from .spmm import spmm
+from .bspmm import bspmm
+from . import torch_sparse_spmm
+
+__all__ = [
+    "ind2ptr",
+    "ptr2ind",
+    "spmm",
+    "bspmm",
+    "segment_csr", "segment_sum_csr", "segment_add_csr", "segment_mean_csr", "segment_min_csr", "segment_max_csr",
+    "segment_reduce",
+    "segment_logsumexp",
+    "segment_coo", "segment_sum_coo", "segment_add_coo", "segment_mean_coo", "segment_min_coo", "segment_max_coo",
+    "torch_sparse_spmm",
+    "Tensor",
+    "OptTensor",
+]
