@@ -61,3 +61,23 @@ def spmm_copy_oracle(indptr, indices, x, reduce="sum", op="copy_lhs"):
         out.scatter_reduce_(0, idx, compute, "amax" if reduce == "max" else "amin", include_self=True)
         out[degree == 0] = 0
     return out.to(values.dtype)
+
+
+def csr_spmm_sum_vectorised(ptr, col, value, mat, edge_chunk=1 << 20):
+    """Weighted CSR SpMM-sum in the value dtype the way the reference's vectorised goldens do it: gather the source
+    rows of a run of edges, scale them, `index_add_` them into the output rows (test/spmm_sum/arch22/golden.py:13-22,
+    test/unified_spmm/arch22/golden.py:42-49).  Edges are processed in chunks so the gathered block stays bounded;
+    this is the function the benchmark times as the CPU baseline.  `mat` is [N, K]; returns [rows, K] in mat's dtype.
+    """
+    ptr = ptr.to(torch.int64)
+    rows_total = ptr.numel() - 1
+    edges = col.numel()
+    rows = edge_rows(ptr, edges)
+    out = torch.zeros((rows_total, mat.size(-1)), dtype=mat.dtype)
+    for start in range(0, edges, edge_chunk):
+        stop = min(start + edge_chunk, edges)
+        block = mat.index_select(0, col[start:stop].long())
+        if value is not None:
+            block.mul_(value[start:stop].reshape(-1, 1).to(mat.dtype))
+        out.index_add_(0, rows[start:stop], block)
+    return out

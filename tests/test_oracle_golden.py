@@ -173,3 +173,14 @@ def test_logsumexp_special_values():
     assert_same(got, torch.tensor([float("inf"), -float("inf"), -float("inf"), 2.0], dtype=torch.float64))
     got = oracle.segment_logsumexp_oracle(src, torch.tensor([0, 2, 4, 4, 5]))
     assert_same(got, torch.tensor([float("inf"), -float("inf"), -float("inf"), 2.0], dtype=torch.float64))
+
+
+def test_vectorised_baseline_equals_oracle():
+    """The function the benchmark times on the CPU computes the same SpMM-sum as the pinned oracle."""
+    from oracle.spmm import csr_spmm_sum_vectorised
+
+    c = load_golden("torch_sparse_spmm")[-8]
+    assert c["reduce"] == "sum" and c["mat"].dim() == 2
+    want, _ = oracle.csr_spmm_oracle(c["ptr"], c["col"], c["value"], c["mat"], "sum")
+    got = csr_spmm_sum_vectorised(c["ptr"], c["col"], c["value"], c["mat"], edge_chunk=97)
+    assert_close(got, want, what="vectorised baseline", scale=20.0)
