@@ -143,23 +143,25 @@ OPSGNN_API int opsgnn_csr_integer_mean(void* out, int out_type, const void* ptr,
 #define OPSGNN_TARGET_COL 2  /* "v"/"dst": indices[e]    */
 
 typedef struct OpsgnnSddmmDesc {
-    int64_t rows;      /* CSR rows                                   */
-    int64_t nnz;       /* edges                                      */
-    int64_t feat;      /* output feature width (dot: reduction width) */
-    int64_t lhs_feat;  /* 1 (broadcast) or feat                      */
-    int64_t rhs_feat;  /* 1 (broadcast) or feat                      */
-    int32_t op;        /* OPSGNN_SDDMM_*                              */
+    int64_t rows;      /* CSR rows                                              */
+    int64_t nnz;       /* edges                                                 */
+    int64_t feat;      /* feature width of both operands (dot: reduction width) */
+    int64_t lhs_rows;  /* rows of lhs (bounds the gather)                       */
+    int64_t rhs_rows;  /* rows of rhs                                           */
+    int32_t op;        /* OPSGNN_SDDMM_*                                        */
     int32_t lhs_target;
     int32_t rhs_target;
-    int32_t index_type; /* OPSGNN_I32 / OPSGNN_I64 (indptr and indices) */
-    int32_t dtype;      /* OPSGNN_F32 / OPSGNN_F16 / OPSGNN_BF16        */
+    int32_t index_type; /* OPSGNN_I32 / OPSGNN_I64 (indptr and indices)         */
+    int32_t dtype;      /* OPSGNN_F32 / OPSGNN_F16 / OPSGNN_BF16                */
 } OpsgnnSddmmDesc;
 
+/* Bytes of scratch (the per-block row plan) for opsgnn_sddmm_csr. */
+OPSGNN_API int opsgnn_sddmm_workspace_bytes(const OpsgnnSddmmDesc* desc, int64_t* bytes);
 /* Replaces SddmmCsr (csrc/npu/sddmm_csr/op_kernel/arch22/sddmm_csr.cpp) as launched by
  * LaunchSddmmCsr (csrc/npu/sddmm_csr/op_host/sddmm_csr.cpp:368-411).
- * dot writes out[nnz]; the other ops write out[nnz, feat].  fp16/bf16 compute in fp32. */
+ * dot writes out[nnz]; the other ops write out[nnz, feat].  fp16/bf16 compute in fp32 and round once. */
 OPSGNN_API int opsgnn_sddmm_csr(const OpsgnnSddmmDesc* desc, const void* indptr, const void* indices, const void* lhs,
-                     const void* rhs, void* out, void* stream);
+                                const void* rhs, void* out, void* workspace, int64_t workspace_bytes, void* stream);
 
 /* dvalue[e, w] = sum_b sum_k mat[b, col[e], k] * grad[b, row(e), k]  (w = 0 when width == 1, else k).
  * Replaces TorchSparseSpmmValueGrad (csrc/npu/torch_sparse_spmm/op_kernel/arch35/torch_sparse_spmm_kernel.h:326-395).

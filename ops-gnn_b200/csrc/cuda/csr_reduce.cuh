@@ -176,8 +176,10 @@ template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK> str
 };
 
 // ---- main kernel ---------------------------------------------------------------------------------------------
-template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK>
-__global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
+// GENERAL = false is the lean instance for calls without weights or with one weight per edge (the weight is staged
+// in shared memory, 1 when absent); GENERAL = true also handles one weight per feature or per feature group.
+template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL>
+__global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
 {
     using TR = Traits<T, O, PtrT, ColT, VEC, NV, RK>;
     using A = typename TR::A;
@@ -248,7 +250,9 @@ __global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
         }
         c = c < 0 ? 0 : (c >= p.src_rows ? p.src_rows - 1 : c);  // validated upstream; never fault on a bad index
         s_off[j] = c * K;
-        if (p.has_val && !p.wide) {
+        if constexpr (!GENERAL) {
+            s_val[j] = p.has_val ? LoadStream(val + a0 + j) : Narrow<T, A>(A(1));
+        } else if (p.has_val && p.wide == 0) {
             s_val[j] = LoadStream(val + a0 + j);
         }
     }
@@ -374,8 +378,10 @@ __global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
         }
     };
 
-    int next_end = s_end[i];
-    while (j < j1) {
+    // Edges are gathered EB at a time regardless of row boundaries, so short rows do not shrink the number of loads in
+    // flight; the batch is then consumed run by run, one run per row that owns part of it.  Every branch below is
+    // uniform across the warp.
+    while (j < j1 || i < i1) {
         const int nb = (j1 - j < EB) ? j1 - j : EB;
         Pack<T, VEC> x[EB][NV];
 #pragma unroll
@@ -390,61 +396,72 @@ __global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
                 }
             }
         }
+        int t_begin = 0;
+        for (;;) {
+            int t_end = nb;
+            bool row_ends = false;
+            if (i < i1) {
+                const int rel = s_end[i] - j;
+                t_end = rel < nb ? rel : nb;
+                row_ends = rel <= nb || nb == 0;  // nb == 0: only row ends are left, always make progress
+            }
 #pragma unroll
-        for (int t = 0; t < EB; ++t) {
-            if (t < nb) {
-                const int e = j + t;
-                while (next_end <= e) {
-                    flush(i);
-                    reset();
-                    dirty = false;
-                    ++i;
-                    next_end = s_end[i];
-                }
-                A w = A(1);
-                if (p.has_val && !p.wide) {
-                    w = Widen<A, T>(s_val[e]);
-                }
-#pragma unroll
-                for (int v = 0; v < NV; ++v) {
-                    if (!live[v]) {
-                        continue;
-                    }
-                    Pack<T, VEC> wv;
-                    if (p.wide == 1) {
-                        wv = LoadGather<T, VEC>(val + (a0 + e) * K + koff[v]);
-                    } else if (p.wide == 2) {
-                        w = Widen<A, T>(__ldg(val + (a0 + e) * p.val_width + group_of[v]));
+            for (int t = 0; t < EB; ++t) {
+                if (t >= t_begin && t < t_end) {
+                    const int e = j + t;
+                    A w = A(1);
+                    if constexpr (!GENERAL) {
+                        w = Widen<A, T>(s_val[e]);  // staged as 1 when the call has no weights
+                    } else if (p.has_val && p.wide == 0) {
+                        w = Widen<A, T>(s_val[e]);
                     }
 #pragma unroll
-                    for (int c = 0; c < VEC; ++c) {
-                        const int q = v * VEC + c;
-                        A value = Widen<A, T>(x[t][v].v[c]);
-                        if (p.wide == 1) {
-                            w = Widen<A, T>(wv.v[c]);
+                    for (int v = 0; v < NV; ++v) {
+                        if (!live[v]) {
+                            continue;
                         }
-                        if constexpr (RK == kSum) {
-                            acc[q] += w * value;
-                        } else if constexpr (RK == kExtremum) {
-                            if (p.has_val) {
-                                value = value * w;
+                        Pack<T, VEC> wv;
+                        if constexpr (GENERAL) {
+                            if (p.wide == 1) {
+                                wv = LoadGather<T, VEC>(val + (a0 + e) * K + koff[v]);
+                            } else if (p.wide == 2) {
+                                w = Widen<A, T>(__ldg(val + (a0 + e) * p.val_width + group_of[v]));
                             }
-                            ExtremumOffer<A>(acc[q], where[q], value, a0 + e, p.is_min, p.extremum);
-                        } else {
-                            LseOffer(acc[q], aux[q], value);
+                        }
+#pragma unroll
+                        for (int c = 0; c < VEC; ++c) {
+                            const int q = v * VEC + c;
+                            A value = Widen<A, T>(x[t][v].v[c]);
+                            if constexpr (GENERAL) {
+                                if (p.wide == 1) {
+                                    w = Widen<A, T>(wv.v[c]);
+                                }
+                            }
+                            if constexpr (RK == kSum) {
+                                acc[q] += w * value;
+                            } else if constexpr (RK == kExtremum) {
+                                value = value * w;  // w == 1 leaves every value, NaN and infinity included, as it is
+                                ExtremumOffer<A>(acc[q], where[q], value, a0 + e, p.is_min, p.extremum);
+                            } else {
+                                LseOffer(acc[q], aux[q], value);
+                            }
                         }
                     }
                 }
+            }
+            if (t_end > t_begin) {
                 dirty = true;
             }
+            t_begin = t_end;
+            if (!row_ends) {
+                break;
+            }
+            flush(i);
+            reset();
+            dirty = false;
+            ++i;
         }
         j += nb;
-    }
-    while (i < i1) {
-        flush(i);
-        reset();
-        dirty = false;
-        ++i;
     }
 
     // ---- carries -------------------------------------------------------------------------------------------------
@@ -641,7 +658,7 @@ __global__ void __launch_bounds__(kThreads) FixupKernel(const Params p)
 }
 
 // ---- host-side launch ----------------------------------------------------------------------------------------
-template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK>
+template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL = true>
 int Launch(Params p, cudaStream_t stream)
 {
     constexpr int TILE = 32 * VEC * NV;
@@ -652,7 +669,7 @@ int Launch(Params p, cudaStream_t stream)
     }
     p.carry_stride = grid_y * TILE;
     const dim3 grid(static_cast<unsigned>(p.num_cta), static_cast<unsigned>(grid_y));
-    ReduceKernel<T, O, PtrT, ColT, VEC, NV, RK><<<grid, kThreads, 0, stream>>>(p);
+    ReduceKernel<T, O, PtrT, ColT, VEC, NV, RK, GENERAL><<<grid, kThreads, 0, stream>>>(p);
     int status = LaunchStatus();
     if (status != OPSGNN_OK) {
         return status;
@@ -670,19 +687,23 @@ int LaunchShaped(const Params& p, cudaStream_t stream)
     const bool vector_ok = sizeof(T) <= 4 && sizeof(T) >= 2 && p.feat % kVec == 0 && Aligned(p.mat, 16) && Aligned(p.out, 16) &&
                            (p.wide != 1 || Aligned(p.val, 16)) && (p.wide != 2 || p.val_group % kVec == 0) &&
                            (RK != kExtremum || Aligned(p.arg, 16));
+    const bool lean = p.wide == 0;  // no weights or one per edge: the instance without per-feature weight code
     if constexpr (sizeof(T) == 4) {
         if (vector_ok && p.feat > 128) {
-            return Launch<T, O, PtrT, ColT, 4, 2, RK>(p, stream);
+            return lean ? Launch<T, O, PtrT, ColT, 4, 2, RK, false>(p, stream)
+                        : Launch<T, O, PtrT, ColT, 4, 2, RK, true>(p, stream);
         }
         if (vector_ok) {
-            return Launch<T, O, PtrT, ColT, 4, 1, RK>(p, stream);
+            return lean ? Launch<T, O, PtrT, ColT, 4, 1, RK, false>(p, stream)
+                        : Launch<T, O, PtrT, ColT, 4, 1, RK, true>(p, stream);
         }
     } else if constexpr (sizeof(T) == 2) {
         if (vector_ok) {
-            return Launch<T, O, PtrT, ColT, 8, 1, RK>(p, stream);
+            return lean ? Launch<T, O, PtrT, ColT, 8, 1, RK, false>(p, stream)
+                        : Launch<T, O, PtrT, ColT, 8, 1, RK, true>(p, stream);
         }
     }
-    return Launch<T, O, PtrT, ColT, 1, 4, RK>(p, stream);
+    return Launch<T, O, PtrT, ColT, 1, 4, RK, true>(p, stream);
 }
 
 }  // namespace csr

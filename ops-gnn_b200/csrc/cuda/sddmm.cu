@@ -1,0 +1,328 @@
+// SDDMM on CSR for sm_100a: out[e] = op(lhs[target_l(e)], rhs[target_r(e)]) for every edge e.
+//
+// Work is split by edges, never by rows: a thread block owns kEdgesPerCta consecutive edges, so power-law rows cost
+// what their edges cost.  The row of an edge is found by a short binary search between the rows of the block's first
+// and last edge (those two come from a per-call plan with one search per block).  Inside a warp, a group of G lanes
+// (G = features / vector width, at most 32) owns one edge at a time and reads both operand rows with 16-byte loads:
+// a 64-float row is one 256-byte request of 16 lanes, and two edges are in flight per warp instruction.  `dot`
+// finishes with a shuffle tree inside the group and the warp writes its 64 results as two coalesced stores; the
+// elementwise ops stream their [nnz, F] result rows with 16-byte stores.  Operand rows selected by the CSR row are
+// re-read from L1 across the row's edges; rows selected by the column are the HBM-bound gather.
+//
+// Algorithmic bytes per launch (dot): nnz*(sizeof(index) + F*sizeof(T) + sizeof(T)) + rows*(sizeof(index) + F*sizeof(T)).
+#include "common.cuh"
+
+namespace opsgnn {
+namespace sddmm {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kEdgesPerWarp = 64;
+constexpr int kEdgesPerCta = kWarps * kEdgesPerWarp;
+
+struct Params {
+    const void* indptr;
+    const void* indices;
+    const void* lhs;
+    const void* rhs;
+    void* out;
+    int64_t* plan;  // row of the first edge of every block, num_cta + 1 entries
+    int64_t rows;
+    int64_t nnz;
+    int64_t feat;
+    int64_t lhs_rows;  // clamp bound of the lhs gather
+    int64_t rhs_rows;
+    int64_t num_cta;
+    int op;
+    int lhs_target;
+    int rhs_target;
+    int group;  // lanes per edge
+};
+
+// Row r with ptr[r] <= edge < ptr[r+1], searched in [lo, hi].
+template <class IndexT>
+__device__ __forceinline__ int64_t RowOf(const IndexT* __restrict__ ptr, int64_t lo, int64_t hi, int64_t edge)
+{
+    while (lo < hi) {
+        const int64_t mid = (lo + hi + 1) >> 1;
+        if (static_cast<int64_t>(ptr[mid]) <= edge) {
+            lo = mid;
+        } else {
+            hi = mid - 1;
+        }
+    }
+    return lo;
+}
+
+template <class IndexT>
+__global__ void PlanKernel(const IndexT* __restrict__ ptr, int64_t rows, int64_t nnz, int64_t num_cta,
+                           int64_t* __restrict__ plan)
+{
+    const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (c > num_cta) {
+        return;
+    }
+    int64_t edge = c * kEdgesPerCta;
+    edge = edge < nnz ? edge : (nnz > 0 ? nnz - 1 : 0);
+    plan[c] = rows > 0 ? RowOf(ptr, 0, rows - 1, edge) : 0;
+}
+
+template <class T, int VEC> __device__ __forceinline__ void Unpack(const Pack<T, VEC>& p, float (&f)[VEC])
+{
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        f[i] = Widen<float, T>(p.v[i]);
+    }
+}
+
+__device__ __forceinline__ float Combine(int op, float a, float b)
+{
+    switch (op) {
+        case OPSGNN_SDDMM_ADD:
+            return a + b;
+        case OPSGNN_SDDMM_SUB:
+            return a - b;
+        case OPSGNN_SDDMM_MUL:
+            return a * b;
+        case OPSGNN_SDDMM_DIV:
+            return a / b;
+        case OPSGNN_SDDMM_COPY_LHS:
+            return a;
+        default:
+            return b;
+    }
+}
+
+template <class T, class IndexT, int VEC, bool DOT>
+__global__ void __launch_bounds__(kThreads) SddmmKernel(const Params p)
+{
+    constexpr int kUnroll = 4;
+    __shared__ int64_t s_lhs[kEdgesPerCta];  // operand row offsets (row index * feat)
+    __shared__ int64_t s_rhs[kEdgesPerCta];
+    __shared__ float s_dot[DOT ? kEdgesPerCta : 1];
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int64_t cta = blockIdx.x;
+    const int64_t e0 = cta * kEdgesPerCta;
+    const int count = static_cast<int>((p.nnz - e0 < kEdgesPerCta) ? p.nnz - e0 : kEdgesPerCta);
+    const IndexT* __restrict__ ptr = static_cast<const IndexT*>(p.indptr);
+    const IndexT* __restrict__ col = static_cast<const IndexT*>(p.indices);
+    const T* __restrict__ lhs = static_cast<const T*>(p.lhs);
+    const T* __restrict__ rhs = static_cast<const T*>(p.rhs);
+    const int64_t F = p.feat;
+    const bool use_lhs = p.op != OPSGNN_SDDMM_COPY_RHS;
+    const bool use_rhs = p.op != OPSGNN_SDDMM_COPY_LHS;
+    const bool need_row = (use_lhs && p.lhs_target == OPSGNN_TARGET_ROW) || (use_rhs && p.rhs_target == OPSGNN_TARGET_ROW);
+    const bool need_col = (use_lhs && p.lhs_target == OPSGNN_TARGET_COL) || (use_rhs && p.rhs_target == OPSGNN_TARGET_COL);
+
+    // ---- operand row of every edge of the block ------------------------------------------------------------------
+    const int64_t row_lo = need_row ? p.plan[cta] : 0;
+    const int64_t row_hi = need_row ? p.plan[cta + 1] : 0;
+    for (int j = tid; j < count; j += kThreads) {
+        const int64_t e = e0 + j;
+        const int64_t r = need_row ? RowOf(ptr, row_lo, row_hi, e) : 0;
+        const int64_t c = need_col ? static_cast<int64_t>(LoadStream(col + e)) : 0;
+        auto pick = [&](int target, int64_t bound) {
+            int64_t v = target == OPSGNN_TARGET_ROW ? r : (target == OPSGNN_TARGET_EDGE ? e : c);
+            v = v < 0 ? 0 : (v >= bound ? bound - 1 : v);  // validated upstream; never fault on a bad index
+            return v * F;
+        };
+        s_lhs[j] = use_lhs ? pick(p.lhs_target, p.lhs_rows) : 0;
+        s_rhs[j] = use_rhs ? pick(p.rhs_target, p.rhs_rows) : 0;
+    }
+    __syncthreads();
+
+    // ---- groups of G lanes walk the warp's edges ---------------------------------------------------------------------
+    const int G = p.group;
+    const int groups = 32 / G;
+    const int g = lane / G;
+    const int gl = lane - g * G;
+    const int w0 = warp * kEdgesPerWarp;
+    const int per_group = kEdgesPerWarp / groups;  // consecutive edges per group keep the row operand hot in L1
+    T* __restrict__ out = static_cast<T*>(p.out);
+
+    for (int t0 = 0; t0 < per_group; t0 += kUnroll) {
+        float partial[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            partial[u] = 0.0f;
+        }
+        for (int64_t f = static_cast<int64_t>(gl) * VEC; f < F; f += static_cast<int64_t>(G) * VEC) {
+            Pack<T, VEC> a[kUnroll], b[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int j = w0 + g * per_group + t0 + u;
+                if (t0 + u < per_group && j < count) {
+                    if (use_lhs) {
+                        a[u] = LoadGather<T, VEC>(lhs + s_lhs[j] + f);
+                    }
+                    if (use_rhs) {
+                        b[u] = LoadGather<T, VEC>(rhs + s_rhs[j] + f);
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                const int j = w0 + g * per_group + t0 + u;
+                if (t0 + u < per_group && j < count) {
+                    float fa[VEC], fb[VEC];
+                    if (use_lhs) {
+                        Unpack<T, VEC>(a[u], fa);
+                    }
+                    if (use_rhs) {
+                        Unpack<T, VEC>(b[u], fb);
+                    }
+                    if constexpr (DOT) {
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) {
+                            partial[u] += fa[i] * fb[i];
+                        }
+                    } else {
+                        Pack<T, VEC> r;
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) {
+                            r.v[i] = Narrow<T, float>(Combine(p.op, use_lhs ? fa[i] : 0.0f, use_rhs ? fb[i] : 0.0f));
+                        }
+                        StoreStream<T, VEC>(out + (e0 + j) * F + f, r);
+                    }
+                }
+            }
+        }
+        if constexpr (DOT) {
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                float v = partial[u];
+                for (int offset = G >> 1; offset > 0; offset >>= 1) {
+                    v += __shfl_xor_sync(0xffffffffu, v, offset, 32);  // offsets below G stay inside the group
+                }
+                const int j = w0 + g * per_group + t0 + u;
+                if (gl == 0 && t0 + u < per_group && j < count) {
+                    s_dot[j] = v;
+                }
+            }
+        }
+    }
+    if constexpr (DOT) {
+        __syncwarp();
+        for (int j = w0 + lane; j < w0 + kEdgesPerWarp && j < count; j += 32) {
+            out[e0 + j] = Narrow<T, float>(s_dot[j]);
+        }
+    }
+}
+
+template <class T, class IndexT, int VEC> int LaunchTyped(const Params& p, cudaStream_t stream)
+{
+    const unsigned grid = static_cast<unsigned>(p.num_cta);
+    if (p.op == OPSGNN_SDDMM_DOT) {
+        SddmmKernel<T, IndexT, VEC, true><<<grid, kThreads, 0, stream>>>(p);
+    } else {
+        SddmmKernel<T, IndexT, VEC, false><<<grid, kThreads, 0, stream>>>(p);
+    }
+    return LaunchStatus();
+}
+
+template <class T, class IndexT> int LaunchVec(Params p, cudaStream_t stream)
+{
+    constexpr int kVec = 16 / sizeof(T);
+    const bool vector_ok = p.feat % kVec == 0 && (p.lhs == nullptr || Aligned(p.lhs, 16)) &&
+                           (p.rhs == nullptr || Aligned(p.rhs, 16)) && (p.op == OPSGNN_SDDMM_DOT || Aligned(p.out, 16));
+    const int vec = vector_ok ? kVec : 1;
+    int group = 1;
+    while (group < 32 && static_cast<int64_t>(group) * vec < p.feat) {
+        group <<= 1;
+    }
+    p.group = group;
+    if (vector_ok) {
+        return LaunchTyped<T, IndexT, kVec>(p, stream);
+    }
+    return LaunchTyped<T, IndexT, 1>(p, stream);
+}
+
+template <class IndexT> int LaunchIndexed(const Params& p, int dtype, cudaStream_t stream)
+{
+    switch (dtype) {
+        case OPSGNN_F32:
+            return LaunchVec<float, IndexT>(p, stream);
+        case OPSGNN_F16:
+            return LaunchVec<__half, IndexT>(p, stream);
+        case OPSGNN_BF16:
+            return LaunchVec<__nv_bfloat16, IndexT>(p, stream);
+        default:
+            return OPSGNN_ERR_UNSUPPORTED;
+    }
+}
+
+}  // namespace sddmm
+}  // namespace opsgnn
+
+using namespace opsgnn;
+using namespace opsgnn::sddmm;
+
+extern "C" int opsgnn_sddmm_workspace_bytes(const OpsgnnSddmmDesc* desc, int64_t* bytes)
+{
+    if (desc == nullptr || bytes == nullptr || desc->nnz < 0) {
+        return OPSGNN_ERR_INVALID;
+    }
+    *bytes = (CeilDiv(desc->nnz, kEdgesPerCta) + 1) * static_cast<int64_t>(sizeof(int64_t));
+    return OPSGNN_OK;
+}
+
+extern "C" int opsgnn_sddmm_csr(const OpsgnnSddmmDesc* desc, const void* indptr, const void* indices, const void* lhs,
+                                const void* rhs, void* out, void* workspace, int64_t workspace_bytes, void* stream)
+{
+    if (desc == nullptr || desc->rows < 0 || desc->nnz < 0 || desc->feat < 1) {
+        return OPSGNN_ERR_INVALID;
+    }
+    const OpsgnnSddmmDesc& d = *desc;
+    if (d.op < OPSGNN_SDDMM_DOT || d.op > OPSGNN_SDDMM_COPY_RHS || d.lhs_target < 0 || d.lhs_target > 2 ||
+        d.rhs_target < 0 || d.rhs_target > 2 || (d.index_type != OPSGNN_I32 && d.index_type != OPSGNN_I64)) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (d.nnz == 0) {
+        return OPSGNN_OK;
+    }
+    const bool use_lhs = d.op != OPSGNN_SDDMM_COPY_RHS;
+    const bool use_rhs = d.op != OPSGNN_SDDMM_COPY_LHS;
+    if (indptr == nullptr || indices == nullptr || out == nullptr || (use_lhs && lhs == nullptr) ||
+        (use_rhs && rhs == nullptr) || (use_lhs && d.lhs_rows < 1) || (use_rhs && d.rhs_rows < 1) || d.rows < 1) {
+        return OPSGNN_ERR_INVALID;
+    }
+    int64_t needed = 0;
+    opsgnn_sddmm_workspace_bytes(desc, &needed);
+    if (workspace == nullptr || workspace_bytes < needed || !Aligned(workspace, 8)) {
+        return OPSGNN_ERR_WORKSPACE;
+    }
+    Params p{};
+    p.indptr = indptr;
+    p.indices = indices;
+    p.lhs = use_lhs ? lhs : nullptr;
+    p.rhs = use_rhs ? rhs : nullptr;
+    p.out = out;
+    p.plan = static_cast<int64_t*>(workspace);
+    p.rows = d.rows;
+    p.nnz = d.nnz;
+    p.feat = d.feat;
+    p.lhs_rows = d.lhs_rows;
+    p.rhs_rows = d.rhs_rows;
+    p.num_cta = CeilDiv(d.nnz, kEdgesPerCta);
+    p.op = d.op;
+    p.lhs_target = d.lhs_target;
+    p.rhs_target = d.rhs_target;
+    if (p.num_cta > 2147483647LL) {
+        return OPSGNN_ERR_LIMIT;
+    }
+    cudaStream_t s = AsStream(stream);
+    const unsigned plan_grid = static_cast<unsigned>(CeilDiv(p.num_cta + 1, 256));
+    if (d.index_type == OPSGNN_I64) {
+        PlanKernel<int64_t><<<plan_grid, 256, 0, s>>>(static_cast<const int64_t*>(indptr), d.rows, d.nnz, p.num_cta, p.plan);
+    } else {
+        PlanKernel<int32_t><<<plan_grid, 256, 0, s>>>(static_cast<const int32_t*>(indptr), d.rows, d.nnz, p.num_cta, p.plan);
+    }
+    int status = LaunchStatus();
+    if (status != OPSGNN_OK) {
+        return status;
+    }
+    return d.index_type == OPSGNN_I64 ? LaunchIndexed<int64_t>(p, d.dtype, s) : LaunchIndexed<int32_t>(p, d.dtype, s);
+}

@@ -112,10 +112,16 @@ std::tuple<at::Tensor, at::Tensor> TorchSparseSpmmForward(at::Tensor ptr, at::Te
     call.reduce = static_cast<int>(reduce);  // 0 sum, 1 mean, 2 min, 3 max: same codes as OPSGNN_REDUCE_*
     call.extremum = OPSGNN_EXTREMUM_IGNORE_NAN;
     const bool integer_mean = reduce == 1 && ot == at::kInt;
-    if (integer_mean) {
-        call.reduce = OPSGNN_REDUCE_SUM;  // the truncating division needs the complete row sum
+    // int8 rows accumulate exactly in int32; a floating mean of them divides the finished sum.
+    const bool widened_mean = reduce == 1 && input == 3 && ot == at::kFloat;
+    if (integer_mean || widened_mean) {
+        call.reduce = OPSGNN_REDUCE_SUM;  // the division needs the complete row sum
     }
     RunCsrReduce(call, "torch_sparse_spmm");
+    if (widened_mean) {
+        auto degree = (ptr.slice(0, 1) - ptr.slice(0, 0, s.m)).clamp_min(1).to(at::kFloat).unsqueeze(-1);
+        out.div_(degree);
+    }
     if (integer_mean) {
         CheckStatus(opsgnn_csr_integer_mean(out.data_ptr(), OPSGNN_I32, ptr.const_data_ptr(), OPSGNN_I64, s.m, s.k,
                                             s.batches, CurrentStream(out)),

@@ -41,6 +41,7 @@ from .segment_coo import (
 )
 from .segment_logsumexp import segment_logsumexp
 from .spmm import spmm
+from .sddmm_csr import sddmm_csr
 from .bspmm import bspmm
 from . import torch_sparse_spmm
 
@@ -49,6 +50,7 @@ __all__ = [
     "ptr2ind",
     "spmm",
     "bspmm",
+    "sddmm_csr",
     "segment_csr", "segment_sum_csr", "segment_add_csr", "segment_mean_csr", "segment_min_csr", "segment_max_csr",
     "segment_reduce",
     "segment_logsumexp",

@@ -24,7 +24,7 @@ GROUPED_SOFTMAX, GROUPED_LOG_SOFTMAX, GROUPED_LOGSUMEXP = range(3)
 EXPORTS = (
     "opsgnn_status_string", "opsgnn_sm_count",
     "opsgnn_csr_plan_bytes", "opsgnn_csr_plan_build", "opsgnn_csr_reduce_workspace_bytes", "opsgnn_csr_reduce",
-    "opsgnn_csr_integer_mean", "opsgnn_sddmm_csr", "opsgnn_spmm_value_grad",
+    "opsgnn_csr_integer_mean", "opsgnn_sddmm_workspace_bytes", "opsgnn_sddmm_csr", "opsgnn_spmm_value_grad",
     "opsgnn_ind2ptr", "opsgnn_ptr2ind", "opsgnn_csr_validate", "opsgnn_permute_values", "opsgnn_index_stats",
     "opsgnn_scatter_workspace_bytes", "opsgnn_scatter",
     "opsgnn_grouped_workspace_bytes", "opsgnn_grouped_forward", "opsgnn_grouped_backward",
@@ -42,7 +42,7 @@ class CsrReduceDesc(Structure):
 
 class SddmmDesc(Structure):
     _fields_ = [
-        ("rows", c_int64), ("nnz", c_int64), ("feat", c_int64), ("lhs_feat", c_int64), ("rhs_feat", c_int64),
+        ("rows", c_int64), ("nnz", c_int64), ("feat", c_int64), ("lhs_rows", c_int64), ("rhs_rows", c_int64),
         ("op", c_int32), ("lhs_target", c_int32), ("rhs_target", c_int32), ("index_type", c_int32),
         ("dtype", c_int32),
     ]
@@ -71,7 +71,9 @@ _PROTOTYPES = {
     "opsgnn_csr_reduce": (c_int, [POINTER(CsrReduceDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "opsgnn_csr_integer_mean": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),
-    "opsgnn_sddmm_csr": (c_int, [POINTER(SddmmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "opsgnn_sddmm_workspace_bytes": (c_int, [POINTER(SddmmDesc), POINTER(c_int64)]),
+    "opsgnn_sddmm_csr": (c_int, [POINTER(SddmmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                 c_void_p]),
     "opsgnn_spmm_value_grad": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
                                        c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "opsgnn_ind2ptr": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
