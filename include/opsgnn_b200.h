@@ -236,20 +236,22 @@ typedef struct OpsgnnGroupedDesc {
     int32_t mode;    /* OPSGNN_GROUPED_*                      */
     int32_t dtype;   /* F32 / F16 / BF16                      */
     int32_t sorted;  /* 1: index is non-decreasing (enables the single-sweep path) */
+    int32_t index_type; /* OPSGNN_I32 (what the reference binding passes) or OPSGNN_I64 */
 } OpsgnnGroupedDesc;
 
 OPSGNN_API int opsgnn_grouped_workspace_bytes(const OpsgnnGroupedDesc* desc, int64_t* bytes);
 /* Replaces ScatterSoftmaxForward / ScatterLogSoftmaxForward / ScatterLogSumExpForward
  * (csrc/npu/scatter_softmax/op_kernel/common/scatter_softmax_kernel_entry.h:218-283) as launched by
  * grouped_softmax::RunForward (csrc/npu/scatter_softmax/common/grouped_softmax_shared.h:178-208).
- * index is int32 [dim_len]. out has src's shape (softmax, log_softmax) or [batch, groups, after] (logsumexp). */
-OPSGNN_API int opsgnn_grouped_forward(const OpsgnnGroupedDesc* desc, const void* src, const int32_t* index, void* out,
-                           void* workspace, int64_t workspace_bytes, void* stream);
+ * index is [dim_len] of desc->index_type. out has src's shape (softmax, log_softmax) or [batch, groups, after]
+ * (logsumexp). */
+OPSGNN_API int opsgnn_grouped_forward(const OpsgnnGroupedDesc* desc, const void* src, const void* index, void* out,
+                                      void* workspace, int64_t workspace_bytes, void* stream);
 /* Replaces the backward launches (scatter_softmax_kernel_entry.h:247-264, 293-357; RunBackward
  * grouped_softmax_shared.h:212-248).  softmax: grad = out*(g - sum_group(out*g)); log_softmax:
  * grad = g - exp(out)*sum_group(g); logsumexp: grad = exp(src - out[group]) * g[group] (src required). */
 OPSGNN_API int opsgnn_grouped_backward(const OpsgnnGroupedDesc* desc, const void* src, const void* out, const void* grad_out,
-                            const int32_t* index, void* grad_src, void* workspace, int64_t workspace_bytes,
+                            const void* index, void* grad_src, void* workspace, int64_t workspace_bytes,
                             void* stream);
 
 #ifdef __cplusplus

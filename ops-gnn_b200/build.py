@@ -31,6 +31,12 @@ NVCC_FLAGS = [
 ]
 
 
+def _nvcc_flags():
+    # OPSGNN_CHECKED=1 builds the self-checking diagnostic variant of the CSR reduce kernels.
+    extra = ["-DOPSGNN_CHECKED"] if os.environ.get("OPSGNN_CHECKED") == "1" else []
+    return NVCC_FLAGS + extra
+
+
 def _nvcc() -> str:
     home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
     return str(Path(home) / "bin" / "nvcc")
@@ -64,7 +70,7 @@ def build_cuda(force: bool = False, workers: int = 8) -> Path:
         obj = OBJ_DIR / (src.stem + ".o")
         objects.append(obj)
         if force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, header_time):
-            jobs.append([_nvcc(), *NVCC_FLAGS, "-I", str(REPO / "include"), "-c", str(src), "-o", str(obj)])
+            jobs.append([_nvcc(), *_nvcc_flags(), "-I", str(REPO / "include"), "-c", str(src), "-o", str(obj)])
     _compile_many(jobs, workers)
     if jobs or not CUDA_LIB.exists():
         _run([_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(CUDA_LIB),

@@ -95,6 +95,34 @@ template <> __device__ __forceinline__ __nv_bfloat16 Narrow<__nv_bfloat16, float
 // ---- aligned vector of VEC elements of T ------------------------------------
 template <class T, int VEC> struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
 
+// Scalar cache-hinted loads.  The toolkit's __ldg / __ldcs overloads for __half and __nv_bfloat16 are non-volatile
+// inline asm, which the compiler may hoist above the branch that guards the pointer (a load through a null `val`
+// pointer then faults even though the source never executes it).  16-bit values are therefore loaded through the
+// unsigned short builtins, which are ordinary loads to the compiler, and bit-cast afterwards.
+template <class T> __device__ __forceinline__ T LoadNc(const T* p)
+{
+    if constexpr (sizeof(T) == 2) {
+        const unsigned short raw = __ldg(reinterpret_cast<const unsigned short*>(p));
+        T out;
+        memcpy(&out, &raw, 2);
+        return out;
+    } else {
+        return __ldg(p);
+    }
+}
+
+template <class T> __device__ __forceinline__ T LoadCs(const T* p)
+{
+    if constexpr (sizeof(T) == 2) {
+        const unsigned short raw = __ldcs(reinterpret_cast<const unsigned short*>(p));
+        T out;
+        memcpy(&out, &raw, 2);
+        return out;
+    } else {
+        return __ldcs(p);
+    }
+}
+
 // Read-only gather through the non-coherent path (rows of the dense operand are never written by the kernel).
 template <class T, int VEC> __device__ __forceinline__ Pack<T, VEC> LoadGather(const T* p)
 {
@@ -112,14 +140,14 @@ template <class T, int VEC> __device__ __forceinline__ Pack<T, VEC> LoadGather(c
         Pack<T, VEC> out;
 #pragma unroll
         for (int i = 0; i < VEC; ++i) {
-            out.v[i] = __ldg(p + i);
+            out.v[i] = LoadNc(p + i);
         }
         return out;
     }
 }
 
 // Streaming load: data read once (edge lists, sorted sources), evict-first in L2.
-template <class T> __device__ __forceinline__ T LoadStream(const T* p) { return __ldcs(p); }
+template <class T> __device__ __forceinline__ T LoadStream(const T* p) { return LoadCs(p); }
 
 // Streaming store of an output row that is not read again by this kernel.
 template <class T, int VEC> __device__ __forceinline__ void StoreStream(T* p, const Pack<T, VEC>& value)

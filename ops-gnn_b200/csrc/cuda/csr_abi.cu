@@ -1,4 +1,6 @@
 // C ABI of the CSR reduce engine: plan construction, scratch sizing and dtype dispatch.
+#include <cstdio>
+
 #include "csr_instances.h"
 
 namespace opsgnn {
@@ -174,6 +176,36 @@ extern "C" int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* pt
 
     const bool index64 = d.ptr_type == OPSGNN_I64;
     cudaStream_t s = AsStream(stream);
+#ifdef OPSGNN_CHECKED
+    // Diagnostic build only: run the launch synchronously and print the first out-of-range access it skipped.
+    static unsigned long long* debug = nullptr;
+    if (debug == nullptr) {
+        OPSGNN_CUDA_TRY(cudaMalloc(&debug, 4 * sizeof(unsigned long long)));
+    }
+    OPSGNN_CUDA_TRY(cudaMemsetAsync(debug, 0, 4 * sizeof(unsigned long long), s));
+    p.debug = debug;
+    struct Report {
+        cudaStream_t s;
+        unsigned long long* debug;
+        const OpsgnnCsrReduceDesc& d;
+        ~Report()
+        {
+            unsigned long long host[4] = {0, 0, 0, 0};
+            const cudaError_t sync = cudaStreamSynchronize(s);
+            cudaMemcpy(host, debug, sizeof(host), cudaMemcpyDeviceToHost);
+            if (host[0] != 0 || sync != cudaSuccess) {
+                fprintf(stderr,
+                        "[opsgnn checked] sync=%d violations=%llu site=%llu index=%lld limit=%lld rows=%lld src_rows=%lld "
+                        "feat=%lld nnz=%lld batches=%lld reduce=%d in=%d out=%d\n",
+                        static_cast<int>(sync), host[0], host[1], static_cast<long long>(host[2]),
+                        static_cast<long long>(host[3]), static_cast<long long>(d.rows),
+                        static_cast<long long>(d.src_rows), static_cast<long long>(d.feat),
+                        static_cast<long long>(d.nnz), static_cast<long long>(d.batches), d.reduce, d.in_type,
+                        d.out_type);
+            }
+        }
+    } report{s, debug, d};
+#endif
     if (col != nullptr) {
         switch (d.in_type) {
             case OPSGNN_F32:
@@ -200,14 +232,15 @@ extern "C" int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* pt
                 return OPSGNN_ERR_UNSUPPORTED;
         }
     }
-    if (val != nullptr || d.out_type != d.in_type) {
+    const bool widened = d.out_type == OPSGNN_F32 && (d.in_type == OPSGNN_F16 || d.in_type == OPSGNN_BF16);
+    if (val != nullptr || (d.out_type != d.in_type && !widened)) {
         return OPSGNN_ERR_UNSUPPORTED;
     }
     switch (d.in_type) {
         case OPSGNN_F32:
         case OPSGNN_F16:
         case OPSGNN_BF16:
-            return RunSegmentFloat(p, d.in_type, index64, kind, s);
+            return RunSegmentFloat(p, d.in_type, index64, kind, widened, s);
         default:
             return RunSegmentOther(p, d.in_type, index64, kind, s);
     }

@@ -13,7 +13,7 @@ int RunSpmmF16(const Params& p, bool index64, int kind, bool out_f32, cudaStream
 int RunSpmmBF16(const Params& p, bool index64, int kind, bool out_f32, cudaStream_t stream);
 int RunSpmmI8(const Params& p, bool index64, int kind, bool out_f32, cudaStream_t stream);
 // Identity gather (segment reductions over consecutive rows).
-int RunSegmentFloat(const Params& p, int dtype, bool ptr64, int kind, cudaStream_t stream);
+int RunSegmentFloat(const Params& p, int dtype, bool ptr64, int kind, bool out_f32, cudaStream_t stream);
 int RunSegmentOther(const Params& p, int dtype, bool ptr64, int kind, cudaStream_t stream);
 
 }  // namespace csr

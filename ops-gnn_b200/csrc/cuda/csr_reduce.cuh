@@ -55,6 +55,7 @@ struct Params {
     int64_t arg_none;
     int64_t num_cta;
     int64_t carry_stride;  // gridDim.y * TILE
+    unsigned long long* debug;  // OPSGNN_CHECKED builds: {violations, first site, index, limit}
     int tiles_per_batch;
     int mean;      // kSum: divide by the row's edge count
     int is_min;    // kExtremum
@@ -64,6 +65,24 @@ struct Params {
     int64_t val_width;  // weights per edge
     int64_t val_group;  // wide == 2: consecutive features that share a weight (feat / val_width)
 };
+
+// Self-checking build (-DOPSGNN_CHECKED): every global access of the reduce kernel is bounds-checked; a bad index is
+// recorded (first site wins) and the access skipped, so a wrong index shows up as a report instead of a fault.
+#ifdef OPSGNN_CHECKED
+__device__ __forceinline__ bool GuardFail(unsigned long long* debug, int site, int64_t index, int64_t limit)
+{
+    if (debug != nullptr && atomicAdd(debug, 1ULL) == 0ULL) {
+        debug[1] = static_cast<unsigned long long>(site);
+        debug[2] = static_cast<unsigned long long>(index);
+        debug[3] = static_cast<unsigned long long>(limit);
+    }
+    return false;
+}
+#define OPSGNN_GUARD(site, index, limit) \
+    (((index) >= 0 && (index) < (limit)) ? true : GuardFail(p.debug, (site), (index), (limit)))
+#else
+#define OPSGNN_GUARD(site, index, limit) true
+#endif
 
 __host__ __device__ inline int64_t NumCta(int64_t rows, int64_t nnz) { return (rows + nnz + kItemsPerCta - 1) / kItemsPerCta; }
 
@@ -179,7 +198,7 @@ template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK> str
 // GENERAL = false is the lean instance for calls without weights or with one weight per edge (the weight is staged
 // in shared memory, 1 when absent); GENERAL = true also handles one weight per feature or per feature group.
 template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL>
-__global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
+__global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
 {
     using TR = Traits<T, O, PtrT, ColT, VEC, NV, RK>;
     using A = typename TR::A;
@@ -223,8 +242,8 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
         return;
     }
     const int64_t d1 = (d0 + kItemsPerCta < total) ? d0 + kItemsPerCta : total;
-    const int64_t row0 = p.plan[cta];
-    const int64_t row1 = p.plan[cta + 1];
+    const int64_t row0 = OPSGNN_GUARD(1, cta + 1, p.num_cta + 1) ? p.plan[cta] : 0;
+    const int64_t row1 = OPSGNN_GUARD(1, cta + 1, p.num_cta + 1) ? p.plan[cta + 1] : 0;
     const int64_t e0 = d0 - row0;  // first edge of the block, counted from `base`
     const int64_t a0 = base + e0;  // the same edge as an absolute position in col / val / the source rows
     int nR = static_cast<int>(row1 - row0);
@@ -234,7 +253,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
     nE = nE < 0 ? 0 : (nE > kItemsPerCta ? kItemsPerCta : nE);
 
     for (int i = tid; i < nR; i += kThreads) {
-        int64_t rel = static_cast<int64_t>(LoadStream(ptr + row0 + 1 + i)) - a0;
+        int64_t rel = (OPSGNN_GUARD(2, row0 + 1 + i, p.rows + 1) ? static_cast<int64_t>(LoadStream(ptr + row0 + 1 + i)) : 0) - a0;
         rel = rel < 0 ? 0 : (rel > nE ? nE : rel);
         s_end[i] = static_cast<int>(rel);
     }
@@ -246,7 +265,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
         if constexpr (kIdentity) {
             c = a0 + j;
         } else {
-            c = static_cast<int64_t>(LoadStream(static_cast<const ColT*>(p.col) + a0 + j));
+            c = OPSGNN_GUARD(3, a0 + j, p.nnz) ? static_cast<int64_t>(LoadStream(static_cast<const ColT*>(p.col) + a0 + j)) : 0;
         }
         c = c < 0 ? 0 : (c >= p.src_rows ? p.src_rows - 1 : c);  // validated upstream; never fault on a bad index
         s_off[j] = c * K;
@@ -359,6 +378,9 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                 packed.v[c] = Narrow<O, A>(value);
             }
             const int64_t at = row * K + koff[v];
+            if (!OPSGNN_GUARD(5, at + VEC - 1, p.rows * K)) {
+                continue;
+            }
             if constexpr (sizeof(O) * VEC == 32) {
                 StoreStream<O, VEC / 2>(out + at, *reinterpret_cast<Pack<O, VEC / 2>*>(&packed.v[0]));
                 StoreStream<O, VEC / 2>(out + at + VEC / 2, *reinterpret_cast<Pack<O, VEC / 2>*>(&packed.v[VEC / 2]));
@@ -390,7 +412,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                 const T* rowp = mat + s_off[j + t];
 #pragma unroll
                 for (int v = 0; v < NV; ++v) {
-                    if (live[v]) {
+                    if (live[v] && OPSGNN_GUARD(4, s_off[j + t] + koff[v] + VEC - 1, p.src_rows * K)) {
                         x[t][v] = LoadGather<T, VEC>(rowp + koff[v]);
                     }
                 }
@@ -425,7 +447,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                             if (p.wide == 1) {
                                 wv = LoadGather<T, VEC>(val + (a0 + e) * K + koff[v]);
                             } else if (p.wide == 2) {
-                                w = Widen<A, T>(__ldg(val + (a0 + e) * p.val_width + group_of[v]));
+                                w = Widen<A, T>(LoadNc(val + (a0 + e) * p.val_width + group_of[v]));
                             }
                         }
 #pragma unroll
@@ -521,6 +543,10 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                 return;
             }
             if (run_row >= nR) {  // the row ends in a later block
+                if (!OPSGNN_GUARD(6, cta * p.carry_stride + static_cast<int64_t>(blockIdx.y) * TILE + f,
+                                  p.num_cta * p.carry_stride)) {
+                    return;
+                }
                 carry_val[f] = run_acc;
                 if constexpr (kHasArg) {
                     carry_arg[f] = run_arg;
@@ -529,6 +555,9 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
             }
             const int64_t row = row0 + run_row;
             const int64_t at = row * K + k;
+            if (!OPSGNN_GUARD(7, at, p.rows * K)) {
+                return;
+            }
             if constexpr (RK == kSum) {
                 A add = run_acc;
                 if (p.mean) {

@@ -58,7 +58,7 @@ class ScatterDesc(Structure):
 class GroupedDesc(Structure):
     _fields_ = [
         ("batch", c_int64), ("dim_len", c_int64), ("after", c_int64), ("groups", c_int64),
-        ("mode", c_int32), ("dtype", c_int32), ("sorted", c_int32),
+        ("mode", c_int32), ("dtype", c_int32), ("sorted", c_int32), ("index_type", c_int32),
     ]
 
 

@@ -50,7 +50,7 @@ def test_torch_sparse_spmm_fixtures(cuda_device):
 def test_csr_spmm_public_api(cuda_device):
     from ops_gnn.torch_sparse_spmm import csr_spmm
 
-    c = load_golden("torch_sparse_spmm")[-6]
+    c = load_golden("torch_sparse_spmm")[-4]  # k = 132, hub row of 600 edges, finite values
     ptr, col, value, mat = (_gpu(c[k], cuda_device) for k in ("ptr", "col", "value", "mat"))
     total = csr_spmm(ptr, col, value, mat, "sum")
     want, _ = oracle.csr_spmm_oracle(c["ptr"], c["col"], c["value"], c["mat"], "sum")
