@@ -95,6 +95,61 @@ template <> __device__ __forceinline__ __nv_bfloat16 Narrow<__nv_bfloat16, float
 // ---- aligned vector of VEC elements of T ------------------------------------
 template <class T, int VEC> struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
 
+// Widen a whole pack / narrow a whole array.  16-bit types go through their 32-bit words (two values per word) so
+// the pack stays in registers; element-wise access to 2-byte members would push it to local memory.
+template <class A, class T, int VEC> __device__ __forceinline__ void Unpack(const Pack<T, VEC>& p, A (&out)[VEC])
+{
+    if constexpr (sizeof(T) == 2 && VEC % 2 == 0 && std::is_same<A, float>::value &&
+                  (std::is_same<T, __half>::value || std::is_same<T, __nv_bfloat16>::value)) {
+        uint32_t words[VEC / 2];
+        memcpy(words, &p, sizeof(words));
+#pragma unroll
+        for (int i = 0; i < VEC / 2; ++i) {
+            if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+                out[2 * i] = __uint_as_float(words[i] << 16);
+                out[2 * i + 1] = __uint_as_float(words[i] & 0xffff0000u);
+            } else {
+                __half2 pair;
+                memcpy(&pair, &words[i], 4);
+                const float2 f = __half22float2(pair);
+                out[2 * i] = f.x;
+                out[2 * i + 1] = f.y;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            out[i] = Widen<A, T>(p.v[i]);
+        }
+    }
+}
+
+template <class O, class A, int VEC> __device__ __forceinline__ Pack<O, VEC> Repack(const A (&in)[VEC])
+{
+    Pack<O, VEC> out;
+    if constexpr (sizeof(O) == 2 && VEC % 2 == 0 && std::is_same<A, float>::value &&
+                  (std::is_same<O, __half>::value || std::is_same<O, __nv_bfloat16>::value)) {
+        uint32_t words[VEC / 2];
+#pragma unroll
+        for (int i = 0; i < VEC / 2; ++i) {
+            if constexpr (std::is_same<O, __nv_bfloat16>::value) {
+                const __nv_bfloat162 pair = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+                memcpy(&words[i], &pair, 4);
+            } else {
+                const __half2 pair = __floats2half2_rn(in[2 * i], in[2 * i + 1]);
+                memcpy(&words[i], &pair, 4);
+            }
+        }
+        memcpy(&out, words, sizeof(words));
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            out.v[i] = Narrow<O, A>(in[i]);
+        }
+    }
+    return out;
+}
+
 // Scalar cache-hinted loads.  The toolkit's __ldg / __ldcs overloads for __half and __nv_bfloat16 are non-volatile
 // inline asm, which the compiler may hoist above the branch that guards the pointer (a load through a null `val`
 // pointer then faults even though the source never executes it).  16-bit values are therefore loaded through the

@@ -191,14 +191,16 @@ template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK> str
     using A = typename AccOf<T>::type;
     static constexpr int kTile = 32 * VEC * NV;
     static constexpr int kElems = VEC * NV;
-    static constexpr int kEdgeBatch = (RK == kSum) ? (NV * VEC * sizeof(T) >= 32 ? 8 : 8) : 4;
+    // Gathered rows in flight per warp before the first use: about 256 bytes per lane for sums (sixteen 16-byte
+    // loads with one vector per lane, eight pairs with two), half of that where positions ride along.
+    static constexpr int kEdgeBatch = (RK == kSum) ? (NV == 1 ? 16 : 8) : (NV == 1 ? 8 : 4);
 };
 
 // ---- main kernel ---------------------------------------------------------------------------------------------
 // GENERAL = false is the lean instance for calls without weights or with one weight per edge (the weight is staged
 // in shared memory, 1 when absent); GENERAL = true also handles one weight per feature or per feature group.
 template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL>
-__global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
+__global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
 {
     using TR = Traits<T, O, PtrT, ColT, VEC, NV, RK>;
     using A = typename TR::A;
@@ -357,7 +359,7 @@ __global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
             if (!live[v]) {
                 continue;
             }
-            Pack<O, VEC> packed;
+            A finished[VEC];
             Pack<int64_t, VEC> packed_arg;
 #pragma unroll
             for (int c = 0; c < VEC; ++c) {
@@ -375,15 +377,17 @@ __global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
                     }
                     packed_arg.v[c] = w < 0 ? p.arg_none : w;
                 }
-                packed.v[c] = Narrow<O, A>(value);
+                finished[c] = value;
             }
+            const Pack<O, VEC> packed = Repack<O, A, VEC>(finished);
             const int64_t at = row * K + koff[v];
             if (!OPSGNN_GUARD(5, at + VEC - 1, p.rows * K)) {
                 continue;
             }
             if constexpr (sizeof(O) * VEC == 32) {
-                StoreStream<O, VEC / 2>(out + at, *reinterpret_cast<Pack<O, VEC / 2>*>(&packed.v[0]));
-                StoreStream<O, VEC / 2>(out + at + VEC / 2, *reinterpret_cast<Pack<O, VEC / 2>*>(&packed.v[VEC / 2]));
+                StoreStream<O, VEC / 2>(out + at, *reinterpret_cast<const Pack<O, VEC / 2>*>(&packed.v[0]));
+                StoreStream<O, VEC / 2>(out + at + VEC / 2,
+                                        *reinterpret_cast<const Pack<O, VEC / 2>*>(&packed.v[VEC / 2]));
             } else {
                 StoreStream<O, VEC>(out + at, packed);
             }
@@ -450,13 +454,21 @@ __global__ void __launch_bounds__(kThreads) ReduceKernel(const Params p)
                                 w = Widen<A, T>(LoadNc(val + (a0 + e) * p.val_width + group_of[v]));
                             }
                         }
+                        A xs[VEC];
+                        Unpack<A, T, VEC>(x[t][v], xs);
+                        A ws[VEC];
+                        if constexpr (GENERAL) {
+                            if (p.wide == 1) {
+                                Unpack<A, T, VEC>(wv, ws);
+                            }
+                        }
 #pragma unroll
                         for (int c = 0; c < VEC; ++c) {
                             const int q = v * VEC + c;
-                            A value = Widen<A, T>(x[t][v].v[c]);
+                            A value = xs[c];
                             if constexpr (GENERAL) {
                                 if (p.wide == 1) {
-                                    w = Widen<A, T>(wv.v[c]);
+                                    w = ws[c];
                                 }
                             }
                             if constexpr (RK == kSum) {

@@ -245,7 +245,7 @@ template <class T> __global__ void __launch_bounds__(kThreads) GradKernel(const 
                 const float lse = Widen<float, T>(fwd[w.stat]);
                 const float weight = __expf(Widen<float, T>(src[i]) - lse);
                 const float g = Widen<float, T>(grad[w.stat]);
-                result = (weight == 0.0f || g == 0.0f) ? 0.0f : weight * g;
+                result = weight * g;  // +inf member or all -inf group: inf - inf = NaN, as torch.logsumexp's gradient
             }
         }
         out[i] = Narrow<T, float>(result);

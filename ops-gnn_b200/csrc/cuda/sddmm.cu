@@ -67,14 +67,6 @@ __global__ void PlanKernel(const IndexT* __restrict__ ptr, int64_t rows, int64_t
     plan[c] = rows > 0 ? RowOf(ptr, 0, rows - 1, edge) : 0;
 }
 
-template <class T, int VEC> __device__ __forceinline__ void Unpack(const Pack<T, VEC>& p, float (&f)[VEC])
-{
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) {
-        f[i] = Widen<float, T>(p.v[i]);
-    }
-}
-
 __device__ __forceinline__ float Combine(int op, float a, float b)
 {
     switch (op) {
@@ -169,10 +161,10 @@ __global__ void __launch_bounds__(kThreads) SddmmKernel(const Params p)
                 if (t0 + u < per_group && j < count) {
                     float fa[VEC], fb[VEC];
                     if (use_lhs) {
-                        Unpack<T, VEC>(a[u], fa);
+                        Unpack<float, T, VEC>(a[u], fa);
                     }
                     if (use_rhs) {
-                        Unpack<T, VEC>(b[u], fb);
+                        Unpack<float, T, VEC>(b[u], fb);
                     }
                     if constexpr (DOT) {
 #pragma unroll
@@ -180,12 +172,12 @@ __global__ void __launch_bounds__(kThreads) SddmmKernel(const Params p)
                             partial[u] += fa[i] * fb[i];
                         }
                     } else {
-                        Pack<T, VEC> r;
+                        float combined[VEC];
 #pragma unroll
                         for (int i = 0; i < VEC; ++i) {
-                            r.v[i] = Narrow<T, float>(Combine(p.op, use_lhs ? fa[i] : 0.0f, use_rhs ? fb[i] : 0.0f));
+                            combined[i] = Combine(p.op, use_lhs ? fa[i] : 0.0f, use_rhs ? fb[i] : 0.0f);
                         }
-                        StoreStream<T, VEC>(out + (e0 + j) * F + f, r);
+                        StoreStream<T, VEC>(out + (e0 + j) * F + f, Repack<T, float, VEC>(combined));
                     }
                 }
             }

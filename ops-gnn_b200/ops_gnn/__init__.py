@@ -43,6 +43,12 @@ from .segment_logsumexp import segment_logsumexp
 from .spmm import spmm
 from .sddmm_csr import sddmm_csr
 from .bspmm import bspmm
+from .scatter import (
+    native_available, scatter, scatter_add, scatter_max, scatter_mean, scatter_min, scatter_mul, scatter_sum,
+)
+from .scatter_softmax import scatter_softmax
+from .scatter_log_softmax import scatter_log_softmax
+from .scatter_logsumexp import scatter_logsumexp
 from . import torch_sparse_spmm
 
 __all__ = [
@@ -55,6 +61,9 @@ __all__ = [
     "segment_reduce",
     "segment_logsumexp",
     "segment_coo", "segment_sum_coo", "segment_add_coo", "segment_mean_coo", "segment_min_coo", "segment_max_coo",
+    "scatter", "scatter_sum", "scatter_add", "scatter_mul", "scatter_mean", "scatter_min", "scatter_max",
+    "native_available",
+    "scatter_softmax", "scatter_log_softmax", "scatter_logsumexp",
     "torch_sparse_spmm",
     "Tensor",
     "OptTensor",
