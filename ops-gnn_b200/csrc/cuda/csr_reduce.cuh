@@ -431,9 +431,11 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                 t_end = rel < nb ? rel : nb;
                 row_ends = rel <= nb || nb == 0;  // nb == 0: only row ends are left, always make progress
             }
-#pragma unroll
-            for (int t = 0; t < EB; ++t) {
-                if (t >= t_begin && t < t_end) {
+            // One gathered edge (slot t of the batch) folded into the accumulators; t is a compile-time constant so
+            // the batch registers are indexed statically.
+            auto consume = [&](auto slot) {
+                constexpr int t = decltype(slot)::value;
+                {
                     const int e = j + t;
                     A w = A(1);
                     if constexpr (!GENERAL) {
@@ -482,7 +484,38 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                         }
                     }
                 }
+            };
+            // Slots [t_begin, t_end) belong to the current row: jump to the first one and fall through until the
+            // run ends, so a batch that spans several rows is not rescanned slot by slot for each of them.
+#define OPSGNN_SLOT(N)                                             \
+    case N:                                                        \
+        if constexpr (N < EB) {                                    \
+            if (N >= t_end) {                                      \
+                break;                                             \
+            }                                                      \
+            consume(std::integral_constant<int, N>{});             \
+        }
+            switch (t_begin) {
+                OPSGNN_SLOT(0)
+                OPSGNN_SLOT(1)
+                OPSGNN_SLOT(2)
+                OPSGNN_SLOT(3)
+                OPSGNN_SLOT(4)
+                OPSGNN_SLOT(5)
+                OPSGNN_SLOT(6)
+                OPSGNN_SLOT(7)
+                OPSGNN_SLOT(8)
+                OPSGNN_SLOT(9)
+                OPSGNN_SLOT(10)
+                OPSGNN_SLOT(11)
+                OPSGNN_SLOT(12)
+                OPSGNN_SLOT(13)
+                OPSGNN_SLOT(14)
+                OPSGNN_SLOT(15)
+                default:
+                    break;
             }
+#undef OPSGNN_SLOT
             if (t_end > t_begin) {
                 dirty = true;
             }

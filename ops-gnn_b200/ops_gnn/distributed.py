@@ -1,0 +1,106 @@
+"""Row-sharded CSR SpMM over the GPUs of one node (one process per GPU, ``torch.distributed`` for the plumbing).
+
+The reference is a single-device library (no collective appears anywhere in it); this module is the multi-GPU form of
+its SpMM path.  Output rows are independent, so the graph is cut into contiguous row ranges that hold equal numbers of
+edges (equal rows would leave the first shard of a power-law graph with most of the work).  Every rank owns one such
+range of the CSR structure and an equal block of the rows of the dense operand ``X``, as a GNN layer would hold them.
+One step is: all-gather the blocks of ``X`` into this GPU's own memory, then run the local SpMM over the rank's rows.
+The gathered matrix lands in local HBM before any kernel reads it; no kernel takes a peer pointer.
+
+``feature_chunks > 1`` splits ``X`` by columns into contiguous chunk-major blocks: the all-gather of chunk ``c + 1``
+runs on a side stream while the SpMM of chunk ``c`` computes, so the transfer hides behind the math tile by tile.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+
+
+def balanced_row_bounds(rowptr: torch.Tensor, parts: int) -> List[int]:
+    """``parts + 1`` row boundaries such that every range ``[b[k], b[k+1])`` holds about ``nnz / parts`` edges."""
+    if parts < 1:
+        raise ValueError("parts must be positive")
+    rows = rowptr.numel() - 1
+    nnz = int(rowptr[-1])
+    targets = torch.tensor([nnz * k // parts for k in range(parts + 1)], dtype=rowptr.dtype, device=rowptr.device)
+    bounds = torch.searchsorted(rowptr.contiguous(), targets, right=False).tolist()
+    bounds[0], bounds[-1] = 0, rows
+    for k in range(1, parts + 1):  # keep the boundaries ordered when many rows are empty
+        bounds[k] = max(bounds[k], bounds[k - 1])
+    return bounds
+
+
+def shard_csr(rowptr: torch.Tensor, col: torch.Tensor, value: Optional[torch.Tensor], first: int,
+              last: int) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """CSR slice of rows ``[first, last)`` with the pointers rebased to zero; columns stay global."""
+    lo, hi = int(rowptr[first]), int(rowptr[last])
+    local_ptr = (rowptr[first:last + 1] - lo).clone()
+    local_val = None if value is None else value[lo:hi].clone()
+    return local_ptr, col[lo:hi].clone(), local_val
+
+
+class RowShardedSpmm:
+    """One rank's share of ``out = A @ X`` (sum reduction) with ``A`` row-sharded and ``X`` block-distributed.
+
+    ``rowptr / col / value`` are the rank's CSR slice (:func:`shard_csr`); ``block_rows`` is the number of rows of
+    ``X`` each rank owns (``N / world``); ``local_spmm(ptr, col, value, x)`` runs the local product (default: the
+    CUDA ``csr_spmm``; the CPU tests pass a stand-in because the product itself has no CPU path).
+    """
+
+    def __init__(self, rowptr, col, value, block_rows: int, feat: int, dtype, device, group=None,
+                 local_spmm: Optional[Callable] = None, feature_chunks: int = 1):
+        import torch.distributed as dist
+
+        self.dist = dist
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.rowptr, self.col, self.value = rowptr, col, value
+        if feat % feature_chunks != 0:
+            raise ValueError("feature_chunks must divide the feature width")
+        self.chunks = feature_chunks
+        self.chunk_width = feat // feature_chunks
+        self.block_rows = block_rows
+        # chunk-major gather buffers: chunk c of the full matrix is a contiguous [N, feat / chunks] tensor
+        self.gathered = [torch.empty((block_rows * self.world, self.chunk_width), dtype=dtype, device=device)
+                         for _ in range(feature_chunks)]
+        if local_spmm is None:
+            from .torch_sparse_spmm import _native
+
+            out_code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dtype]
+            local_spmm = lambda ptr, c, v, x: _native.forward(ptr, c, v, x, 0, out_code)[0]  # noqa: E731
+        self.local_spmm = local_spmm
+        self.side_stream = torch.cuda.Stream(device) if device.type == "cuda" and feature_chunks > 1 else None
+
+    def split_block(self, x_block: torch.Tensor) -> Sequence[torch.Tensor]:
+        """Chunk-major copy of a rank's ``[block_rows, feat]`` block (done once, outside the step)."""
+        if self.chunks == 1:
+            return [x_block.contiguous()]
+        return [part.contiguous() for part in x_block.split(self.chunk_width, dim=1)]
+
+    def _gather(self, chunk: int, block_chunk: torch.Tensor) -> None:
+        self.dist.all_gather_into_tensor(self.gathered[chunk], block_chunk, group=self.group)
+
+    def __call__(self, block_chunks: Sequence[torch.Tensor]) -> List[torch.Tensor]:
+        """Run one step; returns the rank's output rows as one ``[rows, feat / chunks]`` tensor per chunk."""
+        outputs = []
+        if self.side_stream is None:
+            for c, block in enumerate(block_chunks):
+                self._gather(c, block)
+                outputs.append(self.local_spmm(self.rowptr, self.col, self.value, self.gathered[c]))
+            return outputs
+        main = torch.cuda.current_stream()
+        ready = []
+        self.side_stream.wait_stream(main)
+        with torch.cuda.stream(self.side_stream):
+            for c, block in enumerate(block_chunks):
+                self._gather(c, block)
+                event = torch.cuda.Event()
+                event.record(self.side_stream)
+                ready.append(event)
+        for c in range(self.chunks):
+            main.wait_event(ready[c])
+            outputs.append(self.local_spmm(self.rowptr, self.col, self.value, self.gathered[c]))
+        self.side_stream.wait_stream(main)
+        return outputs
