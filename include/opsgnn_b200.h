@@ -163,6 +163,31 @@ OPSGNN_API int opsgnn_sddmm_workspace_bytes(const OpsgnnSddmmDesc* desc, int64_t
 OPSGNN_API int opsgnn_sddmm_csr(const OpsgnnSddmmDesc* desc, const void* indptr, const void* indices, const void* lhs,
                                 const void* rhs, void* out, void* workspace, int64_t workspace_bytes, void* stream);
 
+/*
+ * opsgnn_sddmm_csr without caller-provided scratch.  It has no counterpart in the reference.
+ *
+ * Who needs it: a caller that is not in a position to obtain device memory at call time.  Examples are a plug-in whose
+ * host application has already committed the whole GPU to its own memory pool and hands none of it to plug-ins, and a
+ * latency-critical loop in which any allocator call is forbidden because cudaMalloc / cudaFree may synchronise the
+ * device.  Such a caller owns its inputs and outputs but cannot produce the small row-plan scratch
+ * opsgnn_sddmm_csr asks for, so this variant keeps that scratch in a fixed 256-KiB array inside the library.
+ *
+ * Limits and rules:
+ *  - at most OPSGNN_SDDMM_STATIC_MAX_EDGES = 2^24 edges per call; a larger desc->nnz returns OPSGNN_ERR_LIMIT and
+ *    launches nothing;
+ *  - the array exists once per GPU that loads the library and stays until the process exits;
+ *  - the first call on each device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ *    during start-up, before any stream capture;
+ *  - every call on a device uses the same array and overwrites all of the part it reads, so nothing has to be
+ *    cleared between calls, but two calls whose kernels can overlap on the GPU (different streams) race on it:
+ *    serialise them;
+ *  - the function calls no cudaMalloc, cudaFree or any allocating routine.
+ * Arguments and results are those of opsgnn_sddmm_csr.
+ */
+#define OPSGNN_SDDMM_STATIC_MAX_EDGES (1LL << 24)
+OPSGNN_API int opsgnn_sddmm_csr_static(const OpsgnnSddmmDesc* desc, const void* indptr, const void* indices,
+                                       const void* lhs, const void* rhs, void* out, void* stream);
+
 /* dvalue[e, w] = sum_b sum_k mat[b, col[e], k] * grad[b, row(e), k]  (w = 0 when width == 1, else k).
  * Replaces TorchSparseSpmmValueGrad (csrc/npu/torch_sparse_spmm/op_kernel/arch35/torch_sparse_spmm_kernel.h:326-395).
  * mean == 1 divides by the row's edge count.  grad and out are fp32; mat has dtype mat_type. */

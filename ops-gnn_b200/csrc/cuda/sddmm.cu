@@ -318,3 +318,39 @@ extern "C" int opsgnn_sddmm_csr(const OpsgnnSddmmDesc* desc, const void* indptr,
     }
     return d.index_type == OPSGNN_I64 ? LaunchIndexed<int64_t>(p, d.dtype, s) : LaunchIndexed<int32_t>(p, d.dtype, s);
 }
+
+// ---- variant for callers that cannot allocate ---------------------------------------------------------------------------
+// The per-block row plan lives in a fixed array inside this library instead of caller-provided scratch.  Every GPU
+// that loads the library keeps these 256 KiB until the process exits.
+#define OPSGNN_SDDMM_STATIC_MAX_EDGES (1LL << 24)
+namespace {
+constexpr int64_t kStaticPlanEntries = OPSGNN_SDDMM_STATIC_MAX_EDGES / opsgnn::sddmm::kEdgesPerCta + 1;
+static __device__ __align__(256) int64_t g_static_plan[kStaticPlanEntries];
+constexpr int kMaxDevices = 64;
+void* g_static_plan_address[kMaxDevices] = {nullptr};  // device address of g_static_plan, per device ordinal
+}  // namespace
+
+extern "C" int opsgnn_sddmm_csr_static(const OpsgnnSddmmDesc* desc, const void* indptr, const void* indices,
+                                       const void* lhs, const void* rhs, void* out, void* stream)
+{
+    if (desc == nullptr) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (desc->nnz > OPSGNN_SDDMM_STATIC_MAX_EDGES) {
+        return OPSGNN_ERR_LIMIT;  // more edges than the built-in plan array can describe
+    }
+    int device = -1;
+    OPSGNN_CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) {
+        return OPSGNN_ERR_LIMIT;
+    }
+    if (g_static_plan_address[device] == nullptr) {
+        // In host code `g_static_plan` names a host-side stand-in, not device memory: the address a kernel may use
+        // has to be looked up, with the owning device current (it is: cudaGetDevice above).
+        void* address = nullptr;
+        OPSGNN_CUDA_TRY(cudaGetSymbolAddress(&address, g_static_plan));
+        g_static_plan_address[device] = address;
+    }
+    return opsgnn_sddmm_csr(desc, indptr, indices, lhs, rhs, out, g_static_plan_address[device],
+                            kStaticPlanEntries * static_cast<int64_t>(sizeof(int64_t)), stream);
+}

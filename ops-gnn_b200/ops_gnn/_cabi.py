@@ -24,7 +24,8 @@ GROUPED_SOFTMAX, GROUPED_LOG_SOFTMAX, GROUPED_LOGSUMEXP = range(3)
 EXPORTS = (
     "opsgnn_status_string", "opsgnn_sm_count",
     "opsgnn_csr_plan_bytes", "opsgnn_csr_plan_build", "opsgnn_csr_reduce_workspace_bytes", "opsgnn_csr_reduce",
-    "opsgnn_csr_integer_mean", "opsgnn_sddmm_workspace_bytes", "opsgnn_sddmm_csr", "opsgnn_spmm_value_grad",
+    "opsgnn_csr_integer_mean", "opsgnn_sddmm_workspace_bytes", "opsgnn_sddmm_csr", "opsgnn_sddmm_csr_static",
+    "opsgnn_spmm_value_grad",
     "opsgnn_ind2ptr", "opsgnn_ptr2ind", "opsgnn_csr_validate", "opsgnn_permute_values", "opsgnn_index_stats",
     "opsgnn_scatter_workspace_bytes", "opsgnn_scatter",
     "opsgnn_grouped_workspace_bytes", "opsgnn_grouped_forward", "opsgnn_grouped_backward",
@@ -74,6 +75,7 @@ _PROTOTYPES = {
     "opsgnn_sddmm_workspace_bytes": (c_int, [POINTER(SddmmDesc), POINTER(c_int64)]),
     "opsgnn_sddmm_csr": (c_int, [POINTER(SddmmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                  c_void_p]),
+    "opsgnn_sddmm_csr_static": (c_int, [POINTER(SddmmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "opsgnn_spmm_value_grad": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
                                        c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "opsgnn_ind2ptr": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
