@@ -22,6 +22,8 @@
 // rows*(sizeof(ptr)+K*sizeof(O)) (+ rows*K*8 for arg).
 #pragma once
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace opsgnn {
@@ -187,6 +189,44 @@ __device__ __forceinline__ float LseFinish(float m, float s)
     return m + __logf(s);
 }
 
+// ---- bulk-copy (TMA 1-D) ring ------------------------------------------------------------------------------------
+constexpr int kBulkStages = 3;          // stages per warp
+constexpr int kBulkStageBytes = 4096;   // bytes per stage: 4 rows of 1 KiB, 8 of 512 B, ...
+constexpr int kBulkWarpBytes = kBulkStages * kBulkStageBytes;
+constexpr int kBulkSmemBytes = kWarps * kBulkWarpBytes + kWarps * kBulkStages * 8;
+constexpr uint32_t kBulkSpinLimit = 1u << 22;  // bounded wait on a stage; past it the kernel flags an error and leaves
+
+__device__ __forceinline__ uint32_t SharedAddress(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void MbarExpectTx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Global -> shared bulk copy; source and destination 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void BulkLoad(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK> struct Traits {
     using A = typename AccOf<T>::type;
     static constexpr int kTile = 32 * VEC * NV;
@@ -199,14 +239,21 @@ template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK> str
 // ---- main kernel ---------------------------------------------------------------------------------------------
 // GENERAL = false is the lean instance for calls without weights or with one weight per edge (the weight is staged
 // in shared memory, 1 when absent); GENERAL = true also handles one weight per feature or per feature group.
-template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL>
+//
+// BULK = true gathers the dense rows with the bulk-copy engine instead of per-lane loads: one lane issues one
+// `cp.async.bulk` per gathered row segment (up to 1 KiB) into a per-warp ring of kBulkStages stages in shared
+// memory, completion is tracked by one mbarrier per stage, and the lanes read their 16-byte vectors back with
+// conflict-free shared loads.  Rows in flight then cost shared memory instead of registers: 12 KiB per warp instead
+// of 8, at 16 warps per SM, and the per-edge instruction count drops because one instruction moves a whole row.
+template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL, bool BULK>
 __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
 {
     using TR = Traits<T, O, PtrT, ColT, VEC, NV, RK>;
     using A = typename TR::A;
     constexpr int TILE = TR::kTile;
     constexpr int ELEMS = TR::kElems;
-    constexpr int EB = TR::kEdgeBatch;
+    constexpr int kRowBytes = TILE * static_cast<int>(sizeof(T));  // one staged row segment
+    constexpr int EB = BULK ? kBulkStageBytes / kRowBytes : TR::kEdgeBatch;
     constexpr bool kIdentity = std::is_same<ColT, Identity>::value;
     constexpr bool kHasArg = RK == kExtremum;
 
@@ -215,8 +262,9 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
     __shared__ T s_val[kItemsPerCta];
     __shared__ int s_split[kWarps + 1];
     __shared__ int s_carry_row[kWarps];
-    __shared__ A s_carry[kWarps][TILE];
-    __shared__ int64_t s_carry_arg[kHasArg ? kWarps : 1][kHasArg ? TILE : 1];
+    // Carries of the eight warps.  The bulk variant parks them in each warp's (by then drained) ring instead.
+    __shared__ A s_carry_static[BULK ? 1 : kWarps][BULK ? 1 : TILE];
+    __shared__ int64_t s_carry_arg_static[(kHasArg && !BULK) ? kWarps : 1][(kHasArg && !BULK) ? TILE : 1];
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -294,6 +342,37 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
         s_split[tid] = lo;
     }
     __syncthreads();
+
+    // ---- bulk ring of this warp ------------------------------------------------------------------------------------
+    extern __shared__ __align__(128) unsigned char dyn_smem[];
+    unsigned char* ring = dyn_smem + (BULK ? warp * kBulkWarpBytes : 0);
+    const uint32_t ring_addr = BULK ? SharedAddress(ring) : 0u;
+    const uint32_t bar_addr = BULK ? SharedAddress(dyn_smem + kWarps * kBulkWarpBytes + warp * kBulkStages * 8) : 0u;
+    if constexpr (BULK) {
+        if (lane == 0) {
+#pragma unroll
+            for (int st = 0; st < kBulkStages; ++st) {
+                MbarInit(bar_addr + st * 8, 1);
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncwarp();
+    }
+
+    auto carry_of = [&](int w) -> A* {
+        if constexpr (BULK) {
+            return reinterpret_cast<A*>(dyn_smem + w * kBulkWarpBytes);
+        } else {
+            return s_carry_static[w];
+        }
+    };
+    auto carry_arg_of = [&](int w) -> int64_t* {
+        if constexpr (BULK) {
+            return reinterpret_cast<int64_t*>(dyn_smem + w * kBulkWarpBytes + 2048);
+        } else {
+            return s_carry_arg_static[w];
+        }
+    };
 
     // ---- per-warp walk ---------------------------------------------------------------------------------------
     int dw0 = warp * kItemsPerWarp;
@@ -407,17 +486,65 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
     // Edges are gathered EB at a time regardless of row boundaries, so short rows do not shrink the number of loads in
     // flight; the batch is then consumed run by run, one run per row that owns part of it.  Every branch below is
     // uniform across the warp.
+    // Bulk path: batch b of this warp (edges j0 + b*EB ...) is copied into stage b % kBulkStages.
+    const int j0 = j;
+    const uint32_t seg_bytes =
+        static_cast<uint32_t>((K - kbase < TILE ? K - kbase : static_cast<int64_t>(TILE)) * static_cast<int64_t>(sizeof(T)));
+    auto issue = [&](int b) {
+        const int first = j0 + b * EB;
+        if (first >= j1) {
+            return;
+        }
+        const int n = (j1 - first < EB) ? j1 - first : EB;
+        const int st = b % kBulkStages;
+        if (lane == 0) {
+            MbarExpectTx(bar_addr + st * 8, static_cast<uint32_t>(n) * seg_bytes);
+        }
+        if (lane < n && OPSGNN_GUARD(4, s_off[first + lane] + kbase + TILE - 1, p.src_rows * K + TILE)) {
+            BulkLoad(ring_addr + static_cast<uint32_t>((st * EB + lane) * kRowBytes), mat + s_off[first + lane] + kbase,
+                     seg_bytes, bar_addr + st * 8);
+        }
+    };
+    int batch_id = 0;
+    bool stalled = false;
+    if constexpr (BULK) {
+#pragma unroll
+        for (int st = 0; st < kBulkStages; ++st) {
+            issue(st);
+        }
+    }
     while (j < j1 || i < i1) {
         const int nb = (j1 - j < EB) ? j1 - j : EB;
-        Pack<T, VEC> x[EB][NV];
+        Pack<T, VEC> x[BULK ? 1 : EB][NV];
+        const unsigned char* stage = ring + (batch_id % kBulkStages) * kBulkStageBytes;
+        if constexpr (BULK) {
+            if (nb > 0) {
+                const uint32_t bar = bar_addr + (batch_id % kBulkStages) * 8;
+                const uint32_t parity = static_cast<uint32_t>(batch_id / kBulkStages) & 1u;
+                uint32_t spins = 0;
+                while (!MbarTryWait(bar, parity)) {
+                    if (++spins > kBulkSpinLimit) {  // never expected; leave an error mark instead of hanging
+                        stalled = true;
+                        break;
+                    }
+                }
+                if (stalled) {
+                    if (lane == 0 && p.debug != nullptr) {
+                        atomicAdd(p.debug, 1ULL);
+                    }
+                    break;
+                }
+            }
+        } else {
 #pragma unroll
-        for (int t = 0; t < EB; ++t) {
-            if (t < nb) {
-                const T* rowp = mat + s_off[j + t];
+            for (int t = 0; t < EB; ++t) {
+                if (t < nb) {
+                    const T* rowp = mat + s_off[j + t];
 #pragma unroll
-                for (int v = 0; v < NV; ++v) {
-                    if (live[v] && OPSGNN_GUARD(4, s_off[j + t] + koff[v] + VEC - 1, p.src_rows * K)) {
-                        x[t][v] = LoadGather<T, VEC>(rowp + koff[v]);
+                    for (int v = 0; v < NV; ++v) {
+                        if (live[v] && OPSGNN_GUARD(4, s_off[j + t] + koff[v] + VEC - 1, p.src_rows * K)) {
+                            x[t][v] = LoadGather<T, VEC>(rowp + koff[v]);
+                        }
                     }
                 }
             }
@@ -434,7 +561,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
             // One gathered edge (slot t of the batch) folded into the accumulators; t is a compile-time constant so
             // the batch registers are indexed statically.
             auto consume = [&](auto slot) {
-                constexpr int t = decltype(slot)::value;
+                const int t = static_cast<int>(slot);  // compile-time for the register path, run-time for the ring
                 {
                     const int e = j + t;
                     A w = A(1);
@@ -457,7 +584,13 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                             }
                         }
                         A xs[VEC];
-                        Unpack<A, T, VEC>(x[t][v], xs);
+                        if constexpr (BULK) {
+                            const Pack<T, VEC> staged = LoadPlain<T, VEC>(
+                                reinterpret_cast<const T*>(stage + t * kRowBytes) + (v * 32 + lane) * VEC);
+                            Unpack<A, T, VEC>(staged, xs);
+                        } else {
+                            Unpack<A, T, VEC>(x[decltype(slot)::value][v], xs);
+                        }
                         A ws[VEC];
                         if constexpr (GENERAL) {
                             if (p.wide == 1) {
@@ -495,6 +628,11 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
             }                                                      \
             consume(std::integral_constant<int, N>{});             \
         }
+            if constexpr (BULK) {
+                for (int t = t_begin; t < t_end; ++t) {
+                    consume(t);
+                }
+            } else
             switch (t_begin) {
                 OPSGNN_SLOT(0)
                 OPSGNN_SLOT(1)
@@ -529,6 +667,26 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
             ++i;
         }
         j += nb;
+        if constexpr (BULK) {
+            if (nb > 0) {
+                __syncwarp();  // every lane has read its part of the stage before the stage is refilled
+                issue(batch_id + kBulkStages);
+                ++batch_id;
+            }
+        }
+    }
+    if constexpr (BULK) {
+        if (stalled) {
+            // Give copies still in flight a bounded chance to land before the block's shared memory is released.
+            for (int b = batch_id; b < batch_id + kBulkStages; ++b) {
+                if (j0 + b * EB < j1) {
+                    uint32_t spins = 0;
+                    while (!MbarTryWait(bar_addr + (b % kBulkStages) * 8, static_cast<uint32_t>(b / kBulkStages) & 1u) &&
+                           ++spins <= kBulkSpinLimit) {
+                    }
+                }
+            }
+        }
     }
 
     // ---- carries -------------------------------------------------------------------------------------------------
@@ -543,12 +701,12 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                 const int q = v * VEC + c;
                 const int f = (v * 32 + lane) * VEC + c;
                 if constexpr (RK == kLogSumExp) {
-                    s_carry[warp][f] = LseFinish(acc[q], aux[q]);
+                    carry_of(warp)[f] = LseFinish(acc[q], aux[q]);
                 } else {
-                    s_carry[warp][f] = acc[q];
+                    carry_of(warp)[f] = acc[q];
                 }
                 if constexpr (kHasArg) {
-                    s_carry_arg[warp][f] = where[q];
+                    carry_arg_of(warp)[f] = where[q];
                 }
             }
         }
@@ -635,20 +793,20 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
             if (r < 0) {
                 continue;
             }
-            const A value = s_carry[w][f];
+            const A value = carry_of(w)[f];
             if (r != run_row) {
                 apply();
                 run_row = r;
                 run_acc = value;
                 if constexpr (kHasArg) {
-                    run_arg = s_carry_arg[w][f];
+                    run_arg = carry_arg_of(w)[f];
                 }
             } else if constexpr (RK == kSum) {
                 run_acc += value;
             } else if constexpr (RK == kLogSumExp) {
                 run_acc = LogAddExp(run_acc, value);
             } else {
-                const int64_t a = s_carry_arg[w][f];
+                const int64_t a = carry_arg_of(w)[f];
                 if (a >= 0) {
                     ExtremumOffer<A>(run_acc, run_arg, value, a, p.is_min, p.extremum);
                 }
@@ -732,7 +890,7 @@ __global__ void __launch_bounds__(kThreads) FixupKernel(const Params p)
 }
 
 // ---- host-side launch ----------------------------------------------------------------------------------------
-template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL = true>
+template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL = true, bool BULK = false>
 int Launch(Params p, cudaStream_t stream)
 {
     constexpr int TILE = 32 * VEC * NV;
@@ -743,7 +901,18 @@ int Launch(Params p, cudaStream_t stream)
     }
     p.carry_stride = grid_y * TILE;
     const dim3 grid(static_cast<unsigned>(p.num_cta), static_cast<unsigned>(grid_y));
-    ReduceKernel<T, O, PtrT, ColT, VEC, NV, RK, GENERAL><<<grid, kThreads, 0, stream>>>(p);
+    auto kernel = ReduceKernel<T, O, PtrT, ColT, VEC, NV, RK, GENERAL, BULK>;
+    const size_t dynamic = BULK ? kBulkSmemBytes : 0;
+    if (BULK) {
+        static bool configured[64] = {false};  // per device: opt in to more than 48 KiB of dynamic shared memory
+        int device = 0;
+        OPSGNN_CUDA_TRY(cudaGetDevice(&device));
+        if (device >= 0 && device < 64 && !configured[device]) {
+            OPSGNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
+            configured[device] = true;
+        }
+    }
+    kernel<<<grid, kThreads, dynamic, stream>>>(p);
     int status = LaunchStatus();
     if (status != OPSGNN_OK) {
         return status;
@@ -762,19 +931,26 @@ int LaunchShaped(const Params& p, cudaStream_t stream)
                            (p.wide != 1 || Aligned(p.val, 16)) && (p.wide != 2 || p.val_group % kVec == 0) &&
                            (RK != kExtremum || Aligned(p.arg, 16));
     const bool lean = p.wide == 0;  // no weights or one per edge: the instance without per-feature weight code
+    // Bulk-copy gathers for the lean instances (the hot SpMM / segment paths); OPSGNN_NO_BULK=1 keeps the register
+    // gathers for comparison runs.
+    static const bool bulk_allowed = std::getenv("OPSGNN_NO_BULK") == nullptr;
+    const bool bulk = lean && bulk_allowed;
     if constexpr (sizeof(T) == 4) {
         if (vector_ok && p.feat > 128) {
-            return lean ? Launch<T, O, PtrT, ColT, 4, 2, RK, false>(p, stream)
-                        : Launch<T, O, PtrT, ColT, 4, 2, RK, true>(p, stream);
+            return bulk   ? Launch<T, O, PtrT, ColT, 4, 2, RK, false, true>(p, stream)
+                   : lean ? Launch<T, O, PtrT, ColT, 4, 2, RK, false>(p, stream)
+                          : Launch<T, O, PtrT, ColT, 4, 2, RK, true>(p, stream);
         }
         if (vector_ok) {
-            return lean ? Launch<T, O, PtrT, ColT, 4, 1, RK, false>(p, stream)
-                        : Launch<T, O, PtrT, ColT, 4, 1, RK, true>(p, stream);
+            return bulk   ? Launch<T, O, PtrT, ColT, 4, 1, RK, false, true>(p, stream)
+                   : lean ? Launch<T, O, PtrT, ColT, 4, 1, RK, false>(p, stream)
+                          : Launch<T, O, PtrT, ColT, 4, 1, RK, true>(p, stream);
         }
     } else if constexpr (sizeof(T) == 2) {
         if (vector_ok) {
-            return lean ? Launch<T, O, PtrT, ColT, 8, 1, RK, false>(p, stream)
-                        : Launch<T, O, PtrT, ColT, 8, 1, RK, true>(p, stream);
+            return bulk   ? Launch<T, O, PtrT, ColT, 8, 1, RK, false, true>(p, stream)
+                   : lean ? Launch<T, O, PtrT, ColT, 8, 1, RK, false>(p, stream)
+                          : Launch<T, O, PtrT, ColT, 8, 1, RK, true>(p, stream);
         }
     }
     return Launch<T, O, PtrT, ColT, 1, 4, RK, true>(p, stream);
