@@ -53,6 +53,9 @@ int CheckDesc(const OpsgnnCsrReduceDesc* d)
     if (d->nnz > 0 && d->src_rows == 0) {
         return OPSGNN_ERR_INVALID;
     }
+    if (d->src_rows > 2147483647LL || d->feat > 2147483647LL) {
+        return OPSGNN_ERR_LIMIT;  // staged column ids are 32-bit
+    }
     if (d->extremum < OPSGNN_EXTREMUM_IGNORE_NAN || d->extremum > OPSGNN_EXTREMUM_SEEDED) {
         return OPSGNN_ERR_INVALID;
     }

@@ -31,7 +31,7 @@ namespace csr {
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kItemsPerWarp = 64;
+constexpr int kItemsPerWarp = 128;
 constexpr int kItemsPerCta = kWarps * kItemsPerWarp;
 
 enum ReduceKind { kSum = 0, kExtremum = 1, kLogSumExp = 2 };
@@ -190,8 +190,14 @@ __device__ __forceinline__ float LseFinish(float m, float s)
 }
 
 // ---- bulk-copy (TMA 1-D) ring ------------------------------------------------------------------------------------
-constexpr int kBulkStages = 3;          // stages per warp
-constexpr int kBulkStageBytes = 4096;   // bytes per stage: 4 rows of 1 KiB, 8 of 512 B, ...
+#ifndef OPSGNN_BULK_STAGES
+#define OPSGNN_BULK_STAGES 3
+#endif
+#ifndef OPSGNN_BULK_STAGE_BYTES
+#define OPSGNN_BULK_STAGE_BYTES 4096
+#endif
+constexpr int kBulkStages = OPSGNN_BULK_STAGES;            // stages per warp
+constexpr int kBulkStageBytes = OPSGNN_BULK_STAGE_BYTES;   // bytes per stage: 4 rows of 1 KiB, 8 of 512 B, ...
 constexpr int kBulkWarpBytes = kBulkStages * kBulkStageBytes;
 constexpr int kBulkSmemBytes = kWarps * kBulkWarpBytes + kWarps * kBulkStages * 8;
 constexpr uint32_t kBulkSpinLimit = 1u << 22;  // bounded wait on a stage; past it the kernel flags an error and leaves
@@ -258,8 +264,8 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
     constexpr bool kHasArg = RK == kExtremum;
 
     __shared__ int s_end[kItemsPerCta + 1];
-    __shared__ int64_t s_off[kItemsPerCta];  // col(e) * K
-    __shared__ T s_val[kItemsPerCta];
+    __shared__ int32_t s_col[kItemsPerCta];  // col(e), clamped to the source rows (fewer than 2^31, checked on the host)
+    __shared__ A s_val[kItemsPerCta];  // edge weights, already widened (1 when the call has none)
     __shared__ int s_split[kWarps + 1];
     __shared__ int s_carry_row[kWarps];
     // Carries of the eight warps.  The bulk variant parks them in each warp's (by then drained) ring instead.
@@ -318,11 +324,11 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
             c = OPSGNN_GUARD(3, a0 + j, p.nnz) ? static_cast<int64_t>(LoadStream(static_cast<const ColT*>(p.col) + a0 + j)) : 0;
         }
         c = c < 0 ? 0 : (c >= p.src_rows ? p.src_rows - 1 : c);  // validated upstream; never fault on a bad index
-        s_off[j] = c * K;
+        s_col[j] = static_cast<int32_t>(c);
         if constexpr (!GENERAL) {
-            s_val[j] = p.has_val ? LoadStream(val + a0 + j) : Narrow<T, A>(A(1));
+            s_val[j] = p.has_val ? Widen<A, T>(LoadStream(val + a0 + j)) : A(1);
         } else if (p.has_val && p.wide == 0) {
-            s_val[j] = LoadStream(val + a0 + j);
+            s_val[j] = Widen<A, T>(LoadStream(val + a0 + j));
         }
     }
     __syncthreads();
@@ -390,7 +396,15 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
         koff[v] = kbase + static_cast<int64_t>(v * 32 + lane) * VEC;
-        live[v] = koff[v] < K;
+        live[v] = BULK || koff[v] < K;  // the bulk variant is only launched when the tiles cover K exactly
+    }
+
+    // Per-lane row bases: a gathered vector is lane_base[v] + col * K, one 32x32->64 multiply-add per load.
+    const int K32 = static_cast<int>(K);
+    const T* lane_base[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        lane_base[v] = mat + koff[v];
     }
 
     int64_t group_of[NV];  // wide == 2: weight slot of each owned vector
@@ -500,8 +514,8 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
         if (lane == 0) {
             MbarExpectTx(bar_addr + st * 8, static_cast<uint32_t>(n) * seg_bytes);
         }
-        if (lane < n && OPSGNN_GUARD(4, s_off[first + lane] + kbase + TILE - 1, p.src_rows * K + TILE)) {
-            BulkLoad(ring_addr + static_cast<uint32_t>((st * EB + lane) * kRowBytes), mat + s_off[first + lane] + kbase,
+        if (lane < n && OPSGNN_GUARD(4, static_cast<int64_t>(s_col[first + lane]) * K + kbase + TILE - 1, p.src_rows * K + TILE)) {
+            BulkLoad(ring_addr + static_cast<uint32_t>((st * EB + lane) * kRowBytes), mat + (static_cast<int64_t>(s_col[first + lane]) * K32 + kbase),
                      seg_bytes, bar_addr + st * 8);
         }
     };
@@ -539,11 +553,11 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
 #pragma unroll
             for (int t = 0; t < EB; ++t) {
                 if (t < nb) {
-                    const T* rowp = mat + s_off[j + t];
+                    const int column = s_col[j + t];
 #pragma unroll
                     for (int v = 0; v < NV; ++v) {
-                        if (live[v] && OPSGNN_GUARD(4, s_off[j + t] + koff[v] + VEC - 1, p.src_rows * K)) {
-                            x[t][v] = LoadGather<T, VEC>(rowp + koff[v]);
+                        if (live[v] && OPSGNN_GUARD(4, static_cast<int64_t>(s_col[j + t]) * K + koff[v] + VEC - 1, p.src_rows * K)) {
+                            x[t][v] = LoadGather<T, VEC>(lane_base[v] + static_cast<int64_t>(column) * K32);
                         }
                     }
                 }
@@ -566,9 +580,9 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                     const int e = j + t;
                     A w = A(1);
                     if constexpr (!GENERAL) {
-                        w = Widen<A, T>(s_val[e]);  // staged as 1 when the call has no weights
+                        w = s_val[e];  // staged as 1 when the call has no weights
                     } else if (p.has_val && p.wide == 0) {
-                        w = Widen<A, T>(s_val[e]);
+                        w = s_val[e];
                     }
 #pragma unroll
                     for (int v = 0; v < NV; ++v) {
@@ -937,18 +951,18 @@ int LaunchShaped(const Params& p, cudaStream_t stream)
     const bool bulk = lean && bulk_allowed;
     if constexpr (sizeof(T) == 4) {
         if (vector_ok && p.feat > 128) {
-            return bulk   ? Launch<T, O, PtrT, ColT, 4, 2, RK, false, true>(p, stream)
+            return (bulk && p.feat % 256 == 0) ? Launch<T, O, PtrT, ColT, 4, 2, RK, false, true>(p, stream)
                    : lean ? Launch<T, O, PtrT, ColT, 4, 2, RK, false>(p, stream)
                           : Launch<T, O, PtrT, ColT, 4, 2, RK, true>(p, stream);
         }
         if (vector_ok) {
-            return bulk   ? Launch<T, O, PtrT, ColT, 4, 1, RK, false, true>(p, stream)
+            return (bulk && p.feat % 128 == 0) ? Launch<T, O, PtrT, ColT, 4, 1, RK, false, true>(p, stream)
                    : lean ? Launch<T, O, PtrT, ColT, 4, 1, RK, false>(p, stream)
                           : Launch<T, O, PtrT, ColT, 4, 1, RK, true>(p, stream);
         }
     } else if constexpr (sizeof(T) == 2) {
         if (vector_ok) {
-            return bulk   ? Launch<T, O, PtrT, ColT, 8, 1, RK, false, true>(p, stream)
+            return (bulk && p.feat % 256 == 0) ? Launch<T, O, PtrT, ColT, 8, 1, RK, false, true>(p, stream)
                    : lean ? Launch<T, O, PtrT, ColT, 8, 1, RK, false>(p, stream)
                           : Launch<T, O, PtrT, ColT, 8, 1, RK, true>(p, stream);
         }

@@ -37,7 +37,7 @@ def test_status_strings_and_argument_rejection_need_no_gpu():
     assert b"workspace" in library.opsgnn_status_string(-3)
     size = ctypes.c_int64()
     assert library.opsgnn_csr_plan_bytes(1000, 5000, ctypes.byref(size)) == 0
-    assert size.value == ((1000 + 5000 + 511) // 512 + 1) * 8
+    assert size.value == ((1000 + 5000 + 1023) // 1024 + 1) * 8  # one int64 per block of 1024 items, plus one
     assert library.opsgnn_csr_plan_bytes(-1, 0, ctypes.byref(size)) == -1
     desc = _cabi.CsrReduceDesc(10, 10, 7, 20, 1, 3, 20, 0, 0, _cabi.I64, _cabi.I64, _cabi.F32, _cabi.F32)
     assert library.opsgnn_csr_reduce_workspace_bytes(ctypes.byref(desc), ctypes.byref(size)) == -1  # 7 % 3 != 0
