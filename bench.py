@@ -12,7 +12,8 @@ The line printed by rank 0 carries
   value       whole-job nnz*feat/s with inputs resident in HBM (CUDA events, K steps, max over ranks),
   e2e         the same metric through the public API `ops_gnn.torch_sparse_spmm.csr_spmm` with HOST buffers: the
               pinned-host -> device copies of rowptr/col/value/X and the device -> host copy of the result are inside
-              the timed region,
+              the timed region (N > 1: every rank moves its own CSR slice, block of X and output rows through
+              `ops_gnn.distributed.RowShardedSpmm`),
   roofline    algorithmic bytes of one step / measured step time against the measured HBM copy bandwidth,
   cpu_baseline  the CPU oracle (vectorised restatement of the reference's golden) on a bounded row sample, all host
               threads,
@@ -38,6 +39,9 @@ sys.path.insert(0, os.path.join(ROOT, "ops-gnn_b200"))
 sys.path.insert(0, ROOT)
 
 RMAT = (0.57, 0.19, 0.19, 0.05)
+# dram__bytes_read.sum + dram__bytes_write.sum of one ReduceKernel launch, from the 1-pass ncu capture summarised in
+# profiles/spmm_sum_rmat_s24_f256_dram_traffic.md (a profiler figure, copied here; not measured by this script)
+NCU_DRAM_TRAFFIC = {"rmat_s24_ef16_f256_fp32_spmm_sum": 203.65e9, "rmat_s24_ef16_f256_bf16_spmm_sum": 87.32e9}
 SEED = 20261125 + 4
 
 
@@ -212,20 +216,20 @@ def main():
     out_code = 0 if dtype == torch.float32 else 2
 
     # ---- shard (nnz-balanced contiguous row ranges) ---------------------------------------------------------------------
+    sharded = None
     if distributed:
-        targets = torch.tensor([nnz * r // world for r in range(world + 1)], device=device)
-        bounds = torch.searchsorted(rowptr, targets, right=False).tolist()
-        bounds[0], bounds[-1] = 0, nodes
-        r0, r1 = bounds[rank], bounds[rank + 1]
-        lo, hi = int(rowptr[r0]), int(rowptr[r1])
-        my_ptr = (rowptr[r0:r1 + 1] - lo).clone()
-        my_col, my_val = col[lo:hi].clone(), value[lo:hi].clone()
+        from ops_gnn.distributed import RowShardedSpmm, balanced_row_bounds, shard_csr
+
+        bounds = balanced_row_bounds(rowptr, world)
+        my_ptr, my_col, my_val = shard_csr(rowptr, col, value, bounds[rank], bounds[rank + 1])
         block = nodes // world
         x_block = x[rank * block:(rank + 1) * block].clone()
-        del rowptr, col, value
-        x.zero_()  # proves the gathered copy, not the generator's, feeds the kernel
+        del rowptr, col, value, x
         torch.cuda.empty_cache()
+        sharded = RowShardedSpmm(my_ptr, my_col, my_val, block, args.feat, dtype, device)
+        x = sharded.gathered[0]  # filled by the all-gather of every step, never by the generator
         config["parallelism"] = f"row_shard{world}_allgather_x"
+        config["shard_rows"] = bounds[rank + 1] - bounds[rank]
     else:
         my_ptr, my_col, my_val = rowptr, col, value
         x_block = None
@@ -233,7 +237,7 @@ def main():
 
     def step():
         if distributed:
-            dist.all_gather_into_tensor(x, x_block)
+            return sharded([x_block])[0]
         return forward(my_ptr, my_col, my_val, x, 0, out_code)[0]
 
     def barrier():
@@ -279,7 +283,8 @@ def main():
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32" if elem == 4 else "bf16",
         "data": "synthetic", "config": config, "clocks": clocks,
-        "gpu_launches": args.steps * 2,  # ReduceKernel + FixupKernel per step (the plan is cached after warm-up)
+        # ReduceKernel + FixupKernel per step on every rank (the plan is cached after warm-up); NCCL's kernels not counted
+        "gpu_launches": args.steps * 2 * world,
     }
     if resident_ms is not None:
         result["x_resident"] = {"ms_per_step": resident_ms, "value": nnz * args.feat / (resident_ms * 1e-3),
@@ -296,22 +301,30 @@ def main():
         if not distributed:
             total = algorithmic_bytes(nodes, nnz, args.feat, elem)
             achieved = total / (ms_per_step * 1e-3) / 1e9
+            shape = "4,2" if elem == 4 else "8,1"
             result["roofline"] = {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": None, "peak_source": "measured" if peaks else "fallback",
-                "algorithmic_bytes_per_launch": total,
-                "kernel": "ReduceKernel<float,float,int64,int64,4,2,sum> (+FixupKernel, inside the same timed step)",
+                "traffic": NCU_DRAM_TRAFFIC.get(config["workload"]),
+                "peak_source": "measured" if peaks else "fallback", "algorithmic_bytes_per_launch": total,
+                "kernel": f"opsgnn::ReduceKernel<{args.dtype},{args.dtype},int64,int64,{shape},sum,lean,bulk> "
+                          "(+ FixupKernel, 2.5 % of the step, inside the same timed region)",
             }
 
-    # ---- end to end through the public API with host buffers (N = 1) ---------------------------------------------
-    if not distributed and not args.no_e2e:
-        result["e2e"] = end_to_end(args, csr_spmm, rowptr, col, value, x, nnz)
-    elif distributed:
-        result["e2e"] = None
+    # ---- end to end through the public API with host buffers -----------------------------------------------------------
+    host_inputs = None
+    out = None
+    torch.cuda.empty_cache()
+    if not args.no_e2e:
+        if distributed:
+            result["e2e"] = end_to_end_sharded(args, sharded, x_block, nnz, dist, device)
+        else:
+            result["e2e"], host_inputs = end_to_end(args, csr_spmm, rowptr, col, value, x, nnz)
 
     if rank == 0 and not distributed and not args.no_cpu:
-        host = [t.cpu() for t in (rowptr, col, value)]
-        x_host = x.cpu()
+        if host_inputs is None:
+            host_inputs = [t.cpu() for t in (rowptr, col, value, x)]
+        del rowptr, col, value, x
+        *host, x_host = host_inputs
         sample_ptr, sample_col, sample_val, first, last = cpu_sample(*host, x_host, 1 << 22)
         seconds, threads = time_cpu(sample_ptr, sample_col, sample_val.float(), x_host.float(), repeats=3)
         result["cpu_baseline"] = {
@@ -326,49 +339,132 @@ def main():
     return 0
 
 
-def end_to_end(args, csr_spmm, rowptr, col, value, x, nnz):
-    """K steps of: pinned host -> device copies of every input, csr_spmm, device -> host copy of the result."""
+def host_available_bytes():
     try:
         with open("/proc/meminfo") as handle:
             info = dict(line.split(":") for line in handle.read().splitlines())
-        available = int(info["MemAvailable"].split()[0]) * 1024
+        return int(info["MemAvailable"].split()[0]) * 1024
     except (OSError, KeyError, ValueError):
-        available = None
+        return None
+
+
+def end_to_end(args, csr_spmm, rowptr, col, value, x, nnz):
+    """K steps of: pinned host -> device copies of every input, csr_spmm, device -> host copy of the result.
+
+    The three legs run on three streams with two sets of device staging buffers, so the upload of step k+1 overlaps
+    the product and the download of step k (PCIe is full duplex); every step still uploads all of its inputs and
+    downloads all of its output, and the timed region covers all of it.  Returns (record, pinned host inputs).
+    """
     inputs = (rowptr, col, value, x)
     in_bytes = sum(t.numel() * t.element_size() for t in inputs)
-    out_bytes = (rowptr.numel() - 1) * args.feat * x.element_size()
+    rows = rowptr.numel() - 1
+    out_bytes = rows * args.feat * x.element_size()
+    available = host_available_bytes()
     if available is not None and available < 2 * (in_bytes + out_bytes):
         return {"value": None, "unit": "nnz*feat/s", "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
                 "note": f"skipped: host has {available >> 30} GiB available, pinned staging needs "
-                        f"{(in_bytes + out_bytes) >> 30} GiB"}
+                        f"{(in_bytes + out_bytes) >> 30} GiB"}, None
     pinned = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in inputs]
     for host, dev in zip(pinned, inputs):
         host.copy_(dev)
-    out_host = torch.empty((rowptr.numel() - 1, args.feat), dtype=x.dtype, pin_memory=True)
-    device = x.device
-    staging = [torch.empty_like(t) for t in inputs]  # device buffers reused by every step (no allocation in the loop)
+    out_host = torch.empty((rows, args.feat), dtype=x.dtype, pin_memory=True)
+    slots = 2
+    staging = [[torch.empty_like(t) for t in inputs] for _ in range(slots)]
+    main = torch.cuda.current_stream()
+    upload, download = torch.cuda.Stream(), torch.cuda.Stream()
+    consumed = [None] * slots   # the product that read staging[s] has finished
+    drained = [None] * slots    # the download that read outputs[s] has finished
+    outputs = [None] * slots
+
+    def step(k):
+        s = k % slots
+        with torch.cuda.stream(upload):
+            if consumed[s] is not None:
+                upload.wait_event(consumed[s])
+            for dev, host in zip(staging[s], pinned):
+                dev.copy_(host, non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(upload)
+        main.wait_event(ready)
+        if drained[s] is not None:
+            main.wait_event(drained[s])  # the allocator may hand the old output's memory to the next product
+        outputs[s] = None
+        out = csr_spmm(staging[s][0], staging[s][1], staging[s][2], staging[s][3], "sum")
+        consumed[s] = torch.cuda.Event()
+        consumed[s].record(main)
+        with torch.cuda.stream(download):
+            download.wait_event(consumed[s])
+            out_host.copy_(out, non_blocking=True)
+            drained[s] = torch.cuda.Event()
+            drained[s].record(download)
+        outputs[s] = out
+
+    steps = max(3, min(args.steps, 5))
+    for k in range(slots):
+        step(k)
+    main.wait_stream(download)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record(main)
+    for k in range(steps):
+        step(k)
+    main.wait_stream(download)
+    main.wait_stream(upload)
+    stop.record(main)
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    checksum = float(out_host[:: max(1, out_host.size(0) // 1024)].double().sum())
+    del staging, outputs
+    torch.cuda.empty_cache()
+    return {"value": nnz * args.feat / (ms * 1e-3), "unit": "nnz*feat/s", "ms_per_step": ms, "steps": steps,
+            "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes, "api": "ops_gnn.torch_sparse_spmm.csr_spmm",
+            "overlap": "upload of step k+1 runs beside product and download of step k (2 staging sets, 3 streams)",
+            "result_checksum": checksum}, pinned
+
+
+def end_to_end_sharded(args, sharded, x_block, nnz, dist, device):
+    """N > 1: every rank uploads its CSR slice and its block of X, runs the sharded step, downloads its output rows."""
+    inputs = (sharded.rowptr, sharded.col, sharded.value, x_block)
+    pinned = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in inputs]
+    for host, dev in zip(pinned, inputs):
+        host.copy_(dev)
+    rows = sharded.rowptr.numel() - 1
+    out_host = torch.empty((rows, args.feat), dtype=x_block.dtype, pin_memory=True)
+    staging = [torch.empty_like(t) for t in inputs]
+    saved = (sharded.rowptr, sharded.col, sharded.value)
 
     def step():
         for dev, host in zip(staging, pinned):
             dev.copy_(host, non_blocking=True)
-        out = csr_spmm(staging[0], staging[1], staging[2], staging[3], "sum")
+        sharded.rowptr, sharded.col, sharded.value = staging[0], staging[1], staging[2]
+        out = sharded([staging[3]])[0]
         out_host.copy_(out, non_blocking=True)
-        return out
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
 
     steps = max(3, min(args.steps, 5))
     step()
-    torch.cuda.synchronize()
+    barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(steps):
         step()
     stop.record()
-    torch.cuda.synchronize()
-    ms = start.elapsed_time(stop) / steps
-    checksum = float(out_host[:: max(1, out_host.size(0) // 1024)].double().sum())
+    barrier()
+    sharded.rowptr, sharded.col, sharded.value = saved
+    elapsed = torch.tensor([start.elapsed_time(stop)], device=device)
+    in_bytes = torch.tensor([sum(t.numel() * t.element_size() for t in inputs)], device=device)
+    out_bytes = torch.tensor([rows * args.feat * x_block.element_size()], device=device)
+    dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    dist.all_reduce(in_bytes)
+    dist.all_reduce(out_bytes)
+    ms = float(elapsed.item()) / steps
     return {"value": nnz * args.feat / (ms * 1e-3), "unit": "nnz*feat/s", "ms_per_step": ms, "steps": steps,
-            "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes, "api": "ops_gnn.torch_sparse_spmm.csr_spmm",
-            "result_checksum": checksum}
+            "h2d_bytes_per_step": int(in_bytes.item()), "d2h_bytes_per_step": int(out_bytes.item()),
+            "api": "ops_gnn.distributed.RowShardedSpmm", "note": "bytes are summed over ranks; time is the max over ranks"}
 
 
 def reference_arm(args, rowptr, col, value, x, config):
