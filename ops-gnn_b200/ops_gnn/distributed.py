@@ -17,17 +17,30 @@ from typing import Callable, List, Optional, Sequence, Tuple
 import torch
 
 
-def balanced_row_bounds(rowptr: torch.Tensor, parts: int) -> List[int]:
-    """``parts + 1`` row boundaries such that every range ``[b[k], b[k+1])`` holds about ``nnz / parts`` edges."""
+def balanced_row_bounds(rowptr: torch.Tensor, parts: int, row_cost: float = 0.0) -> List[int]:
+    """``parts + 1`` row boundaries such that every range ``[b[k], b[k+1])`` holds an equal share of the work.
+
+    Work is ``edges + row_cost * rows``: with ``row_cost = 0`` the ranges hold ``nnz / parts`` edges each; for an SpMM
+    use ``row_cost = 1`` (writing one output row moves as many bytes as gathering one row of the dense operand), so a
+    shard of many short rows is not handed as many edges as a shard of few hub rows.
+    """
     if parts < 1:
         raise ValueError("parts must be positive")
+    if row_cost < 0:
+        raise ValueError("row_cost must not be negative")
     rows = rowptr.numel() - 1
-    nnz = int(rowptr[-1])
-    targets = torch.tensor([nnz * k // parts for k in range(parts + 1)], dtype=rowptr.dtype, device=rowptr.device)
-    bounds = torch.searchsorted(rowptr.contiguous(), targets, right=False).tolist()
+    work = rowptr.contiguous()
+    if row_cost:
+        work = work.to(torch.float64) + row_cost * torch.arange(rows + 1, dtype=torch.float64, device=rowptr.device)
+    total = float(work[-1]) if rows >= 0 and work.numel() else 0.0
+    targets = torch.tensor([total * k / parts for k in range(parts + 1)], dtype=torch.float64, device=rowptr.device)
+    if not row_cost:
+        targets = torch.tensor([int(total) * k // parts for k in range(parts + 1)], dtype=rowptr.dtype,
+                               device=rowptr.device)
+    bounds = torch.searchsorted(work, targets.to(work.dtype), right=False).tolist()
     bounds[0], bounds[-1] = 0, rows
     for k in range(1, parts + 1):  # keep the boundaries ordered when many rows are empty
-        bounds[k] = max(bounds[k], bounds[k - 1])
+        bounds[k] = min(max(bounds[k], bounds[k - 1]), rows)
     return bounds
 
 

@@ -92,3 +92,14 @@ def test_balanced_bounds_properties():
         assert all(a <= b for a, b in zip(bounds, bounds[1:]))
     empty = balanced_row_bounds(torch.zeros(5, dtype=torch.int64), 2)
     assert empty[0] == 0 and empty[-1] == 4
+    # with a cost per row, a graph without edges is split by rows, and short-row shards get fewer edges
+    assert balanced_row_bounds(torch.zeros(5, dtype=torch.int64), 2, row_cost=1.0) == [0, 2, 4]
+    degree = torch.cat([torch.full((10,), 100), torch.ones(1000, dtype=torch.int64)])
+    skewed = torch.zeros(degree.numel() + 1, dtype=torch.int64)
+    skewed[1:] = degree.cumsum(0)
+    by_edges = balanced_row_bounds(skewed, 2)
+    by_work = balanced_row_bounds(skewed, 2, row_cost=1.0)
+    assert by_edges == [0, 10, 1010]
+    assert by_work[1] > by_edges[1]
+    work = [int(skewed[b] - skewed[a]) + (b - a) for a, b in zip(by_work, by_work[1:])]
+    assert abs(work[0] - work[1]) <= 101
