@@ -66,6 +66,7 @@ struct Params {
     int wide;      // 0: one weight per edge (or none); 1: one per (edge, feature); 2: one per (edge, feature group)
     int64_t val_width;  // weights per edge
     int64_t val_group;  // wide == 2: consecutive features that share a weight (feat / val_width)
+    int lanes_per_row;  // narrow instance: lanes that share one gathered row (a power of two below 32)
 };
 
 // Self-checking build (-DOPSGNN_CHECKED): every global access of the reduce kernel is bounds-checked; a bad index is
@@ -181,12 +182,60 @@ __device__ __forceinline__ void LseOffer(float& m, float& s, float x)
     }
 }
 
+// Merge of two online states (maximum, sum of exp(x - maximum)); symmetric in its operands.  The maximum is never
+// NaN (a NaN input lands in the sum), equal maxima - infinite ones included - add their sums unscaled.
+__device__ __forceinline__ void LseMerge(float& m, float& s, float other_m, float other_s)
+{
+    const bool mine_high = m >= other_m;
+    const float hi = mine_high ? m : other_m;
+    const float lo = mine_high ? other_m : m;
+    const float s_hi = mine_high ? s : other_s;
+    const float s_lo = mine_high ? other_s : s;
+    const float scale = (hi == lo) ? 1.0f : __expf(lo - hi);
+    m = hi;
+    s = s_hi + s_lo * scale;
+}
+
 __device__ __forceinline__ float LseFinish(float m, float s)
 {
     if (s == 0.0f) {
         return m;  // empty: m = -inf
     }
     return m + __logf(s);
+}
+
+// Merge of two partial extrema taken under the same rule over disjoint edge sets: the result is what one scan over
+// the union in edge order would have selected (first NaN under the propagating rule, else the extremum with the
+// smallest position among ties).  Symmetric in its two operands.
+template <class A>
+__device__ __forceinline__ void ExtremumMerge(A& acc, int64_t& arg, A other, int64_t other_arg, int is_min, int rule)
+{
+    if (other_arg < 0) {
+        return;
+    }
+    if (arg < 0) {
+        acc = other;
+        arg = other_arg;
+        return;
+    }
+    if (rule == OPSGNN_EXTREMUM_PROPAGATE_NAN && (IsNan(acc) || IsNan(other))) {
+        if (IsNan(other) && (!IsNan(acc) || other_arg < arg)) {
+            acc = other;
+            arg = other_arg;
+        }
+        return;
+    }
+    const bool better = is_min ? (other < acc) : (other > acc);
+    if (better || (other == acc && other_arg < arg)) {
+        acc = other;
+        arg = other_arg;
+    }
+}
+
+template <class V> __device__ __forceinline__ V ShuffleXor(V v, int mask) { return __shfl_xor_sync(0xffffffffu, v, mask); }
+__device__ __forceinline__ int64_t ShuffleXor(int64_t v, int mask)
+{
+    return static_cast<int64_t>(__shfl_xor_sync(0xffffffffu, static_cast<long long>(v), mask));
 }
 
 // ---- bulk-copy (TMA 1-D) ring ------------------------------------------------------------------------------------
@@ -251,9 +300,14 @@ template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK> str
 // memory, completion is tracked by one mbarrier per stage, and the lanes read their 16-byte vectors back with
 // conflict-free shared loads.  Rows in flight then cost shared memory instead of registers: 12 KiB per warp instead
 // of 8, at 16 warps per SM, and the per-edge instruction count drops because one instruction moves a whole row.
-template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL, bool BULK>
+//
+// NARROW = true (bulk only, NV == 1) is for rows narrower than one warp of 16-byte vectors (16 to 256 bytes, a power
+// of two): p.lanes_per_row lanes share a gathered row and the 32 / lanes_per_row lane groups take different edges of
+// the same run, so no lane idles; the groups' partial results are merged with shuffles when the row ends.
+template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL, bool BULK, bool NARROW = false>
 __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
 {
+    static_assert(!NARROW || (BULK && NV == 1 && !GENERAL), "the narrow layout exists for lean bulk instances only");
     using TR = Traits<T, O, PtrT, ColT, VEC, NV, RK>;
     using A = typename TR::A;
     constexpr int TILE = TR::kTile;
@@ -280,6 +334,13 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
     const int tile = blockIdx.y - batch * p.tiles_per_batch;
     const int64_t kbase = static_cast<int64_t>(tile) * TILE;
     const int64_t K = p.feat;
+    // Lane layout: `lpg` lanes share one gathered row; group `grp` takes every `groups`-th edge of a run.
+    const int lpg = NARROW ? p.lanes_per_row : 32;
+    const int groups = NARROW ? 32 / lpg : 1;
+    const int grp = NARROW ? lane / lpg : 0;
+    const int lane_in = NARROW ? (lane & (lpg - 1)) : lane;
+    const int row_bytes = NARROW ? lpg * VEC * static_cast<int>(sizeof(T)) : kRowBytes;  // one staged row segment
+    const int eb = NARROW ? kBulkStageBytes / row_bytes : EB;                            // rows per stage / batch
 
     const PtrT* __restrict__ ptr = static_cast<const PtrT*>(p.ptr);
     const T* __restrict__ mat = static_cast<const T*>(p.mat) + static_cast<int64_t>(batch) * p.src_rows * K;
@@ -395,7 +456,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
     int64_t koff[NV];
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
-        koff[v] = kbase + static_cast<int64_t>(v * 32 + lane) * VEC;
+        koff[v] = kbase + static_cast<int64_t>(v * 32 + lane_in) * VEC;
         live[v] = BULK || koff[v] < K;  // the bulk variant is only launched when the tiles cover K exactly
     }
 
@@ -434,8 +495,31 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
     reset();
     bool dirty = false;
 
+    // Narrow layout: fold the lane groups' partial results into every group (xor butterfly, the same value in all).
+    auto merge_groups = [&]() {
+        if constexpr (NARROW) {
+            for (int off = lpg; off < 32; off <<= 1) {
+#pragma unroll
+                for (int q = 0; q < ELEMS; ++q) {
+                    if constexpr (RK == kSum) {
+                        acc[q] += ShuffleXor(acc[q], off);
+                    } else if constexpr (RK == kLogSumExp) {
+                        const A other_max = ShuffleXor(acc[q], off);
+                        const A other_sum = ShuffleXor(aux[q], off);
+                        LseMerge(acc[q], aux[q], other_max, other_sum);
+                    } else {
+                        const A other = ShuffleXor(acc[q], off);
+                        const int64_t other_arg = ShuffleXor(where[q], off);
+                        ExtremumMerge<A>(acc[q], where[q], other, other_arg, p.is_min, p.extremum);
+                    }
+                }
+            }
+        }
+    };
+
     auto flush = [&](int local_row) {
         const int64_t row = row0 + local_row;
+        merge_groups();
         A scale = A(1);
         bool divide = false;
         if constexpr (RK == kSum) {
@@ -449,7 +533,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
         }
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
-            if (!live[v]) {
+            if (!live[v] || grp != 0) {
                 continue;
             }
             A finished[VEC];
@@ -505,18 +589,30 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
     const uint32_t seg_bytes =
         static_cast<uint32_t>((K - kbase < TILE ? K - kbase : static_cast<int64_t>(TILE)) * static_cast<int64_t>(sizeof(T)));
     auto issue = [&](int b) {
-        const int first = j0 + b * EB;
+        const int first = j0 + b * eb;
         if (first >= j1) {
             return;
         }
-        const int n = (j1 - first < EB) ? j1 - first : EB;
+        const int n = (j1 - first < eb) ? j1 - first : eb;
         const int st = b % kBulkStages;
         if (lane == 0) {
             MbarExpectTx(bar_addr + st * 8, static_cast<uint32_t>(n) * seg_bytes);
         }
-        if (lane < n && OPSGNN_GUARD(4, static_cast<int64_t>(s_col[first + lane]) * K + kbase + TILE - 1, p.src_rows * K + TILE)) {
-            BulkLoad(ring_addr + static_cast<uint32_t>((st * EB + lane) * kRowBytes), mat + (static_cast<int64_t>(s_col[first + lane]) * K32 + kbase),
-                     seg_bytes, bar_addr + st * 8);
+        if constexpr (kIdentity) {
+            // Consecutive source rows: when a row segment is the whole row, the stage is one contiguous copy.
+            if (p.tiles_per_batch == 1 && a0 + first + n <= p.src_rows) {
+                if (lane == 0) {
+                    BulkLoad(ring_addr + static_cast<uint32_t>(st * kBulkStageBytes), mat + (a0 + first) * K,
+                             static_cast<uint32_t>(n) * seg_bytes, bar_addr + st * 8);
+                }
+                return;
+            }
+        }
+        for (int r = lane; r < n; r += 32) {
+            if (OPSGNN_GUARD(4, static_cast<int64_t>(s_col[first + r]) * K + kbase + TILE - 1, p.src_rows * K + TILE)) {
+                BulkLoad(ring_addr + static_cast<uint32_t>(st * kBulkStageBytes + r * row_bytes),
+                         mat + (static_cast<int64_t>(s_col[first + r]) * K32 + kbase), seg_bytes, bar_addr + st * 8);
+            }
         }
     };
     int batch_id = 0;
@@ -528,7 +624,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
         }
     }
     while (j < j1 || i < i1) {
-        const int nb = (j1 - j < EB) ? j1 - j : EB;
+        const int nb = (j1 - j < eb) ? j1 - j : eb;
         Pack<T, VEC> x[BULK ? 1 : EB][NV];
         const unsigned char* stage = ring + (batch_id % kBulkStages) * kBulkStageBytes;
         if constexpr (BULK) {
@@ -600,7 +696,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                         A xs[VEC];
                         if constexpr (BULK) {
                             const Pack<T, VEC> staged = LoadPlain<T, VEC>(
-                                reinterpret_cast<const T*>(stage + t * kRowBytes) + (v * 32 + lane) * VEC);
+                                reinterpret_cast<const T*>(stage + t * row_bytes) + (v * 32 + lane_in) * VEC);
                             Unpack<A, T, VEC>(staged, xs);
                         } else {
                             Unpack<A, T, VEC>(x[decltype(slot)::value][v], xs);
@@ -642,7 +738,13 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
             }                                                      \
             consume(std::integral_constant<int, N>{});             \
         }
-            if constexpr (BULK) {
+            if constexpr (NARROW) {
+                for (int tt = t_begin; tt < t_end; tt += groups) {
+                    if (tt + grp < t_end) {
+                        consume(tt + grp);
+                    }
+                }
+            } else if constexpr (BULK) {
                 for (int t = t_begin; t < t_end; ++t) {
                     consume(t);
                 }
@@ -693,7 +795,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
         if (stalled) {
             // Give copies still in flight a bounded chance to land before the block's shared memory is released.
             for (int b = batch_id; b < batch_id + kBulkStages; ++b) {
-                if (j0 + b * EB < j1) {
+                if (j0 + b * eb < j1) {
                     uint32_t spins = 0;
                     while (!MbarTryWait(bar_addr + (b % kBulkStages) * 8, static_cast<uint32_t>(b / kBulkStages) & 1u) &&
                            ++spins <= kBulkSpinLimit) {
@@ -708,12 +810,15 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
         s_carry_row[warp] = dirty ? i1 : -1;
     }
     if (dirty) {
+        merge_groups();
+    }
+    if (dirty && grp == 0) {
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
 #pragma unroll
             for (int c = 0; c < VEC; ++c) {
                 const int q = v * VEC + c;
-                const int f = (v * 32 + lane) * VEC + c;
+                const int f = (v * 32 + lane_in) * VEC + c;
                 if constexpr (RK == kLogSumExp) {
                     carry_of(warp)[f] = LseFinish(acc[q], aux[q]);
                 } else {
@@ -904,7 +1009,8 @@ __global__ void __launch_bounds__(kThreads) FixupKernel(const Params p)
 }
 
 // ---- host-side launch ----------------------------------------------------------------------------------------
-template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL = true, bool BULK = false>
+template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL = true, bool BULK = false,
+          bool NARROW = false>
 int Launch(Params p, cudaStream_t stream)
 {
     constexpr int TILE = 32 * VEC * NV;
@@ -915,10 +1021,10 @@ int Launch(Params p, cudaStream_t stream)
     }
     p.carry_stride = grid_y * TILE;
     const dim3 grid(static_cast<unsigned>(p.num_cta), static_cast<unsigned>(grid_y));
-    auto kernel = ReduceKernel<T, O, PtrT, ColT, VEC, NV, RK, GENERAL, BULK>;
+    auto kernel = ReduceKernel<T, O, PtrT, ColT, VEC, NV, RK, GENERAL, BULK, NARROW>;
     const size_t dynamic = BULK ? kBulkSmemBytes : 0;
     if (BULK) {
-        static bool configured[64] = {false};  // per device: opt in to more than 48 KiB of dynamic shared memory
+        static bool configured[64] = {false};  // per device and instance: opt in to more than 48 KiB of dynamic shared memory
         int device = 0;
         OPSGNN_CUDA_TRY(cudaGetDevice(&device));
         if (device >= 0 && device < 64 && !configured[device]) {
@@ -949,6 +1055,15 @@ int LaunchShaped(const Params& p, cudaStream_t stream)
     // gathers for comparison runs.
     static const bool bulk_allowed = std::getenv("OPSGNN_NO_BULK") == nullptr;
     const bool bulk = lean && bulk_allowed;
+    if constexpr (sizeof(T) == 4 || sizeof(T) == 2) {
+        // Rows of 16 to 256 bytes (a power of two): several edges per warp instruction instead of idle lanes.
+        const int64_t vectors = p.feat / kVec;
+        if (bulk && vector_ok && vectors >= 1 && vectors <= 16 && (vectors & (vectors - 1)) == 0) {
+            Params narrow = p;
+            narrow.lanes_per_row = static_cast<int>(vectors);
+            return Launch<T, O, PtrT, ColT, kVec, 1, RK, false, true, true>(narrow, stream);
+        }
+    }
     if constexpr (sizeof(T) == 4) {
         if (vector_ok && p.feat > 128) {
             return (bulk && p.feat % 256 == 0) ? Launch<T, O, PtrT, ColT, 4, 2, RK, false, true>(p, stream)

@@ -197,6 +197,51 @@ template <class T> __global__ void __launch_bounds__(kThreads) ApplyLseKernel(co
     }
 }
 
+// Vector form for batch == 1 and `after` a multiple of the 16-byte vector width: one thread owns VEC consecutive
+// features of one row, so the group id and the row decomposition are computed once per 16 bytes of src.
+template <class T, int VEC> __global__ void __launch_bounds__(kThreads) ApplyLseVecKernel(const Params p)
+{
+    const T* __restrict__ src = static_cast<const T*>(p.src);
+    T* __restrict__ out = static_cast<T*>(p.out);
+    const int64_t per_row = p.after / VEC;
+    const int64_t vectors = p.dim_len * per_row;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const bool small = vectors < (1LL << 32);
+    for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < vectors; v += stride) {
+        int64_t pos;
+        if (small) {  // 32-bit division where it is exact
+            pos = static_cast<unsigned>(v) / static_cast<unsigned>(per_row);
+        } else {
+            pos = v / per_row;
+        }
+        const int64_t a = (v - pos * per_row) * VEC;
+        const int64_t g = GroupOf(p, pos);
+        float result[VEC];
+        if (g >= 0 && g < p.groups) {
+            float x[VEC];
+            Unpack<float, T, VEC>(LoadGather<T, VEC>(src + v * VEC), x);
+            const float* __restrict__ lse_row = p.top + g * p.after + a;
+#pragma unroll
+            for (int c = 0; c < VEC; c += 4) {
+                const float4 lse4 = __ldg(reinterpret_cast<const float4*>(lse_row + c));
+                const float lse[4] = {lse4.x, lse4.y, lse4.z, lse4.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float shifted = x[c + q] - lse[q];
+                    const float value = p.mode == OPSGNN_GROUPED_SOFTMAX ? __expf(shifted) : shifted;
+                    result[c + q] = isfinite(lse[q]) ? value : NAN;  // same rule as the scalar kernel above
+                }
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < VEC; ++c) {
+                result[c] = 0.0f;
+            }
+        }
+        StoreStream<T, VEC>(out + v * VEC, Repack<T, float, VEC>(result));
+    }
+}
+
 template <class T> __global__ void CastKernel(const float* __restrict__ in, T* __restrict__ out, int64_t n)
 {
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -327,7 +372,12 @@ template <class T> int Forward(const OpsgnnGroupedDesc& d, Params p, char* works
         if (d.mode == OPSGNN_GROUPED_LOGSUMEXP) {
             CastKernel<T><<<Grid(l.stats), kThreads, 0, s>>>(p.top, static_cast<T*>(p.out), l.stats);
         } else {
-            ApplyLseKernel<T><<<Grid(n), kThreads, 0, s>>>(p);
+            constexpr int kVec = 16 / sizeof(T);
+            if (d.batch == 1 && d.after % kVec == 0 && Aligned(p.src, 16) && Aligned(p.out, 16) && Aligned(p.top, 16)) {
+                ApplyLseVecKernel<T, kVec><<<Grid(n / kVec), kThreads, 0, s>>>(p);
+            } else {
+                ApplyLseKernel<T><<<Grid(n), kThreads, 0, s>>>(p);
+            }
         }
         return LaunchStatus();
     }

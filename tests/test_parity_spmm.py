@@ -138,7 +138,8 @@ def test_spmm_copy_fixtures(cuda_device):
         if c["reduce"] in ("max", "min"):
             assert_same(got, c["out"], what)
         else:
-            assert_close(got, c["out"], what=what, scale=8.0)
+            # sums of quotients by N(0,1) draws hold terms far larger than the result: looser relative bound
+            assert_close(got, c["out"], what=what, scale=32.0 if c.get("op") == "div" else 8.0)
 
 
 def test_fused_attention_aggregation(cuda_device):
@@ -180,3 +181,60 @@ def test_backward_matches_dense(cuda_device):
     want_value = (upstream.cpu().double() @ mat.detach().cpu().double().t())[r, c]
     assert_close(mat.grad, want_mat.float(), what="d mat", scale=8.0)
     assert_close(value.grad, want_value.float(), what="d value", scale=8.0)
+
+
+@pytest.mark.parametrize("dtype,widths,tol", [
+    (torch.float32, (4, 8, 16, 32, 64), 1e-5),
+    (torch.float16, (8, 16, 32, 64, 128), 2e-3),
+    (torch.bfloat16, (8, 64, 128), 1e-2),
+])
+def test_narrow_rows(cuda_device, dtype, widths, tol):
+    """Rows of 16 to 256 bytes: several edges share one warp instruction and lane groups are merged at row ends.
+    Ties, NaN and infinities are planted so the merge has to reproduce the first-occurrence and NaN rules."""
+    import ops_gnn
+    from ops_gnn.torch_sparse_spmm import csr_spmm
+
+    gen = torch.Generator().manual_seed(11)
+    rows, cols = 6000, 5000
+    degree = torch.randint(0, 40, (rows,), generator=gen)
+    degree[5], degree[6], degree[4000] = 30000, 0, 7000
+    ptr = torch.zeros(rows + 1, dtype=torch.int64)
+    ptr[1:] = degree.cumsum(0)
+    col = torch.randint(0, cols, (int(ptr[-1]),), generator=gen)
+    value = torch.rand(col.numel(), generator=gen).to(dtype)
+    for k in widths:
+        mat = torch.randn(cols, k, generator=gen)
+        mat = (mat * 4).round() / 4          # many exact ties
+        mat[17, 0], mat[18, k - 1], mat[19, 1] = float("nan"), float("inf"), float("-inf")
+        mat = mat.to(dtype)
+        dev = [t.to(cuda_device) for t in (ptr, col, value, mat)]
+        got = csr_spmm(*dev, "sum")
+        again = csr_spmm(*dev, "sum")
+        assert torch.equal(torch.nan_to_num(got), torch.nan_to_num(again)), "the result must not depend on scheduling"
+        want, _ = oracle.csr_spmm_oracle(ptr, col, value, mat, "sum", torch.float64)
+        finite = torch.isfinite(want)
+        assert torch.equal(torch.isnan(got.cpu()), torch.isnan(want)), f"NaN pattern, K={k}"
+        assert torch.equal(got.cpu().double()[torch.isinf(want)], want[torch.isinf(want)]), f"infinities, K={k}"
+        clean_mat = torch.nan_to_num(mat.float(), nan=0.0, posinf=0.0, neginf=0.0)
+        clean_got = torch.where(finite, got.cpu().float(), torch.zeros(()))
+        clean_want, _ = oracle.csr_spmm_oracle(ptr, col, value, clean_mat.to(dtype), "sum", torch.float64)
+        _conditioned_close(clean_got, ptr, col, value, clean_mat, torch.where(finite, clean_want, torch.zeros((), dtype=torch.float64)),
+                           tol, f"sum K={k} {dtype}")
+        for reduce in ("max", "min"):
+            best, where = csr_spmm(dev[0], dev[1], None, dev[3], reduce)
+            want, want_arg = oracle.csr_spmm_oracle(ptr, col, None, mat, reduce)
+            assert_same(best, want, f"{reduce} K={k} {dtype}")
+            assert_same(where, want_arg, f"{reduce} arg K={k} {dtype}")
+        if dtype != torch.bfloat16:
+            unweighted = ops_gnn.spmm(dev[0], dev[1], dev[3], reduce="max")
+            assert_same(unweighted, oracle.spmm_copy_oracle(ptr, col, mat, "max"), f"spmm max K={k}")
+        # the segment forms of the same engine (consecutive source rows, contiguous stage copies)
+        src = mat[col]                      # [E, k]
+        d_src = src.to(cuda_device)
+        seg_want, seg_arg = oracle.segment_csr_oracle(src, ptr, "max", return_arg=True)
+        seg_got = ops_gnn.segment_max_csr(d_src, dev[0])
+        assert_same(seg_got[0], seg_want, f"segment max K={k}")
+        assert_same(seg_got[1], seg_arg, f"segment max arg K={k}")
+        lse = ops_gnn.segment_logsumexp(d_src, dev[0])
+        lse_want = oracle.segment_logsumexp_oracle(src, ptr)
+        assert_close(lse, lse_want.to(lse.dtype), what=f"segment_logsumexp K={k} {dtype}", scale=4.0)
