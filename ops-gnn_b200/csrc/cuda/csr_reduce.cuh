@@ -249,6 +249,10 @@ constexpr int kBulkStages = OPSGNN_BULK_STAGES;            // stages per warp
 constexpr int kBulkStageBytes = OPSGNN_BULK_STAGE_BYTES;   // bytes per stage: 4 rows of 1 KiB, 8 of 512 B, ...
 constexpr int kBulkWarpBytes = kBulkStages * kBulkStageBytes;
 constexpr int kBulkSmemBytes = kWarps * kBulkWarpBytes + kWarps * kBulkStages * 8;
+// Per-group weights (one per edge and feature group, e.g. attention heads) ride along with the rows of a stage: the
+// weights of the stage's edges are contiguous in memory, so one more bulk copy per stage brings them in.
+constexpr int kBulkWeightBytes = 128;  // per stage: rows per stage x weights per edge x sizeof(T) must fit
+constexpr int kBulkSmemBytesWeighted = kBulkSmemBytes + kWarps * kBulkStages * kBulkWeightBytes;
 constexpr uint32_t kBulkSpinLimit = 1u << 22;  // bounded wait on a stage; past it the kernel flags an error and leaves
 
 __device__ __forceinline__ uint32_t SharedAddress(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -319,7 +323,8 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
 
     __shared__ int s_end[kItemsPerCta + 1];
     __shared__ int32_t s_col[kItemsPerCta];  // col(e), clamped to the source rows (fewer than 2^31, checked on the host)
-    __shared__ A s_val[kItemsPerCta];  // edge weights, already widened (1 when the call has none)
+    // edge weights, already widened (1 when the call has none); the weighted bulk instance keeps its weights in the ring
+    __shared__ A s_val[(GENERAL && BULK) ? 1 : kItemsPerCta];
     __shared__ int s_split[kWarps + 1];
     __shared__ int s_carry_row[kWarps];
     // Carries of the eight warps.  The bulk variant parks them in each warp's (by then drained) ring instead.
@@ -388,8 +393,10 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
         s_col[j] = static_cast<int32_t>(c);
         if constexpr (!GENERAL) {
             s_val[j] = p.has_val ? Widen<A, T>(LoadStream(val + a0 + j)) : A(1);
-        } else if (p.has_val && p.wide == 0) {
-            s_val[j] = Widen<A, T>(LoadStream(val + a0 + j));
+        } else if constexpr (!BULK) {
+            if (p.has_val && p.wide == 0) {
+                s_val[j] = Widen<A, T>(LoadStream(val + a0 + j));
+            }
         }
     }
     __syncthreads();
@@ -415,6 +422,11 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
     unsigned char* ring = dyn_smem + (BULK ? warp * kBulkWarpBytes : 0);
     const uint32_t ring_addr = BULK ? SharedAddress(ring) : 0u;
     const uint32_t bar_addr = BULK ? SharedAddress(dyn_smem + kWarps * kBulkWarpBytes + warp * kBulkStages * 8) : 0u;
+    // weighted bulk instance: [stage][edge][weight] behind the barriers, kBulkWeightBytes per stage
+    const T* weight_ring = reinterpret_cast<const T*>(dyn_smem + kWarps * kBulkWarpBytes + kWarps * kBulkStages * 8 +
+                                                      ((GENERAL && BULK) ? warp * kBulkStages * kBulkWeightBytes : 0));
+    const uint32_t weight_addr = (GENERAL && BULK) ? SharedAddress(weight_ring) : 0u;
+    const uint32_t weight_row_bytes = static_cast<uint32_t>(p.val_width * static_cast<int64_t>(sizeof(T)));
     if constexpr (BULK) {
         if (lane == 0) {
 #pragma unroll
@@ -596,7 +608,13 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
         const int n = (j1 - first < eb) ? j1 - first : eb;
         const int st = b % kBulkStages;
         if (lane == 0) {
-            MbarExpectTx(bar_addr + st * 8, static_cast<uint32_t>(n) * seg_bytes);
+            if constexpr (GENERAL) {
+                MbarExpectTx(bar_addr + st * 8, static_cast<uint32_t>(n) * (seg_bytes + weight_row_bytes));
+                BulkLoad(weight_addr + static_cast<uint32_t>(st * kBulkWeightBytes), val + (a0 + first) * p.val_width,
+                         static_cast<uint32_t>(n) * weight_row_bytes, bar_addr + st * 8);
+            } else {
+                MbarExpectTx(bar_addr + st * 8, static_cast<uint32_t>(n) * seg_bytes);
+            }
         }
         if constexpr (kIdentity) {
             // Consecutive source rows: when a row segment is the whole row, the stage is one contiguous copy.
@@ -677,8 +695,10 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                     A w = A(1);
                     if constexpr (!GENERAL) {
                         w = s_val[e];  // staged as 1 when the call has no weights
-                    } else if (p.has_val && p.wide == 0) {
-                        w = s_val[e];
+                    } else if constexpr (!BULK) {
+                        if (p.has_val && p.wide == 0) {
+                            w = s_val[e];
+                        }
                     }
 #pragma unroll
                     for (int v = 0; v < NV; ++v) {
@@ -686,7 +706,10 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                             continue;
                         }
                         Pack<T, VEC> wv;
-                        if constexpr (GENERAL) {
+                        if constexpr (GENERAL && BULK) {  // one weight per (edge, feature group), staged with the rows
+                            w = Widen<A, T>(weight_ring[(batch_id % kBulkStages) * (kBulkWeightBytes / static_cast<int>(sizeof(T))) +
+                                                        t * static_cast<int>(p.val_width) + static_cast<int>(group_of[v])]);
+                        } else if constexpr (GENERAL) {
                             if (p.wide == 1) {
                                 wv = LoadGather<T, VEC>(val + (a0 + e) * K + koff[v]);
                             } else if (p.wide == 2) {
@@ -1022,13 +1045,13 @@ int Launch(Params p, cudaStream_t stream)
     p.carry_stride = grid_y * TILE;
     const dim3 grid(static_cast<unsigned>(p.num_cta), static_cast<unsigned>(grid_y));
     auto kernel = ReduceKernel<T, O, PtrT, ColT, VEC, NV, RK, GENERAL, BULK, NARROW>;
-    const size_t dynamic = BULK ? kBulkSmemBytes : 0;
+    const size_t dynamic = BULK ? (GENERAL ? kBulkSmemBytesWeighted : kBulkSmemBytes) : 0;
     if (BULK) {
         static bool configured[64] = {false};  // per device and instance: opt in to more than 48 KiB of dynamic shared memory
         int device = 0;
         OPSGNN_CUDA_TRY(cudaGetDevice(&device));
         if (device >= 0 && device < 64 && !configured[device]) {
-            OPSGNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
+            OPSGNN_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dynamic)));
             configured[device] = true;
         }
     }
@@ -1062,6 +1085,22 @@ int LaunchShaped(const Params& p, cudaStream_t stream)
             Params narrow = p;
             narrow.lanes_per_row = static_cast<int>(vectors);
             return Launch<T, O, PtrT, ColT, kVec, 1, RK, false, true, true>(narrow, stream);
+        }
+    }
+    // One weight per (edge, feature group): bulk gathers with the weights staged beside the rows, when a stage's
+    // weights fit their slot and every copy is 16-byte aligned.
+    auto weighted_bulk = [&](int tile, int rows_per_stage) {
+        const int64_t row_bytes = p.val_width * static_cast<int64_t>(sizeof(T));
+        return bulk_allowed && p.wide == 2 && RK == kSum && vector_ok && p.feat % tile == 0 && Aligned(p.val, 16) &&
+               row_bytes % 16 == 0 && rows_per_stage * row_bytes <= kBulkWeightBytes;
+    };
+    if constexpr (RK == kSum && sizeof(T) == 4) {
+        if (weighted_bulk(256, kBulkStageBytes / 1024)) {
+            return Launch<T, O, PtrT, ColT, 4, 2, RK, true, true>(p, stream);
+        }
+    } else if constexpr (RK == kSum && sizeof(T) == 2) {
+        if (weighted_bulk(256, kBulkStageBytes / 512)) {
+            return Launch<T, O, PtrT, ColT, 8, 1, RK, true, true>(p, stream);
         }
     }
     if constexpr (sizeof(T) == 4) {
