@@ -129,8 +129,8 @@ template <class A> __device__ __forceinline__ bool IsNan(A v) { return v != v; }
 
 // Extremum update; `arg < 0` means nothing selected yet.  Earlier items are offered first, so strict compares
 // keep the first occurrence among ties.
-template <class A>
-__device__ __forceinline__ void ExtremumOffer(A& acc, int64_t& arg, A v, int64_t where, int is_min, int rule)
+template <class A, class I = int64_t>
+__device__ __forceinline__ void ExtremumOffer(A& acc, I& arg, A v, I where, int is_min, int rule)
 {
     const bool better = is_min ? (v < acc) : (v > acc);
     bool take;
@@ -207,8 +207,8 @@ __device__ __forceinline__ float LseFinish(float m, float s)
 // Merge of two partial extrema taken under the same rule over disjoint edge sets: the result is what one scan over
 // the union in edge order would have selected (first NaN under the propagating rule, else the extremum with the
 // smallest position among ties).  Symmetric in its two operands.
-template <class A>
-__device__ __forceinline__ void ExtremumMerge(A& acc, int64_t& arg, A other, int64_t other_arg, int is_min, int rule)
+template <class A, class I = int64_t>
+__device__ __forceinline__ void ExtremumMerge(A& acc, I& arg, A other, I other_arg, int is_min, int rule)
 {
     if (other_arg < 0) {
         return;
@@ -488,7 +488,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
 
     A acc[ELEMS];
     A aux[RK == kLogSumExp ? ELEMS : 1];       // sum of exponentials
-    int64_t where[kHasArg ? ELEMS : 1];        // selected edge, -1 for none
+    int where[kHasArg ? ELEMS : 1];            // selected edge as an index into the block's staged edges, -1 for none
     const A seed = (RK == kExtremum) ? ExtremumSeed<A, T>(p.is_min, p.extremum) : A(0);
     auto reset = [&]() {
 #pragma unroll
@@ -521,8 +521,8 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                         LseMerge(acc[q], aux[q], other_max, other_sum);
                     } else {
                         const A other = ShuffleXor(acc[q], off);
-                        const int64_t other_arg = ShuffleXor(where[q], off);
-                        ExtremumMerge<A>(acc[q], where[q], other, other_arg, p.is_min, p.extremum);
+                        const int other_arg = ShuffleXor(where[q], off);
+                        ExtremumMerge<A, int>(acc[q], where[q], other, other_arg, p.is_min, p.extremum);
                     }
                 }
             }
@@ -560,11 +560,11 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                 } else if constexpr (RK == kLogSumExp) {
                     value = LseFinish(value, aux[v * VEC + c]);
                 } else {
-                    const int64_t w = where[v * VEC + c];
+                    const int w = where[v * VEC + c];
                     if (w < 0) {
                         value = A(0);
                     }
-                    packed_arg.v[c] = w < 0 ? p.arg_none : w;
+                    packed_arg.v[c] = w < 0 ? p.arg_none : a0 + w;
                 }
                 finished[c] = value;
             }
@@ -743,7 +743,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                                 acc[q] += w * value;
                             } else if constexpr (RK == kExtremum) {
                                 value = value * w;  // w == 1 leaves every value, NaN and infinity included, as it is
-                                ExtremumOffer<A>(acc[q], where[q], value, a0 + e, p.is_min, p.extremum);
+                                ExtremumOffer<A, int>(acc[q], where[q], value, e, p.is_min, p.extremum);
                             } else {
                                 LseOffer(acc[q], aux[q], value);
                             }
@@ -848,7 +848,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                     carry_of(warp)[f] = acc[q];
                 }
                 if constexpr (kHasArg) {
-                    carry_arg_of(warp)[f] = where[q];
+                    carry_arg_of(warp)[f] = where[q] < 0 ? int64_t(-1) : a0 + where[q];
                 }
             }
         }
