@@ -312,6 +312,8 @@ template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, boo
 __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
 {
     static_assert(!NARROW || (BULK && NV == 1 && !GENERAL), "the narrow layout exists for lean bulk instances only");
+    static_assert(NARROW || (BULK ? kBulkStageBytes / (32 * VEC * NV * static_cast<int>(sizeof(T))) : 16) <= 16,
+                  "the slot dispatch below enumerates sixteen slots");
     using TR = Traits<T, O, PtrT, ColT, VEC, NV, RK>;
     using A = typename TR::A;
     constexpr int TILE = TR::kTile;
@@ -767,12 +769,12 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                         consume(tt + grp);
                     }
                 }
-            } else if constexpr (BULK) {
+            } else if constexpr (BULK && EB > 4) {
                 for (int t = t_begin; t < t_end; ++t) {
                     consume(t);
                 }
             } else
-            switch (t_begin) {
+            switch (t_begin) {  // register path and four-row bulk stages: slots are compile-time, offsets immediates
                 OPSGNN_SLOT(0)
                 OPSGNN_SLOT(1)
                 OPSGNN_SLOT(2)
