@@ -165,6 +165,9 @@ def parse():
     parser.add_argument("--edge-factor", type=int, default=16)
     parser.add_argument("--feat", type=int, default=256)
     parser.add_argument("--dtype", default="fp32", choices=("fp32", "bf16"))
+    parser.add_argument("--exchange", default="allgather", choices=("allgather", "halo"),
+                        help="N > 1: all-gather of X, or an all-to-all of only the rows each shard references")
+    parser.add_argument("--row-cost", type=float, default=4.0, help="N > 1: cost of one output row in edges (shard balance)")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     return parser.parse_args()
@@ -218,18 +221,31 @@ def main():
     # ---- shard (nnz-balanced contiguous row ranges) ---------------------------------------------------------------------
     sharded = None
     if distributed:
-        from ops_gnn.distributed import RowShardedSpmm, balanced_row_bounds, shard_csr
+        from ops_gnn.distributed import HaloShardedSpmm, RowShardedSpmm, balanced_row_bounds, shard_csr
 
-        bounds = balanced_row_bounds(rowptr, world, row_cost=1.0)
+        # a row end costs the kernel about four edges on this graph (measured per rank: 0.13 ns per edge, 0.6 ns per row)
+        bounds = balanced_row_bounds(rowptr, world, row_cost=args.row_cost)
         my_ptr, my_col, my_val = shard_csr(rowptr, col, value, bounds[rank], bounds[rank + 1])
-        block = nodes // world
-        x_block = x[rank * block:(rank + 1) * block].clone()
-        del rowptr, col, value, x
-        torch.cuda.empty_cache()
-        sharded = RowShardedSpmm(my_ptr, my_col, my_val, block, args.feat, dtype, device)
-        x = sharded.gathered[0]  # filled by the all-gather of every step, never by the generator
-        config["parallelism"] = f"row_shard{world}_allgather_x"
         config["shard_rows"] = bounds[rank + 1] - bounds[rank]
+        if args.exchange == "halo":
+            # X is owned by the same row ranges as the output (a layer's output rows are the next layer's input)
+            x_block = x[bounds[rank]:bounds[rank + 1]].clone()
+            del rowptr, col, value, x
+            torch.cuda.empty_cache()
+            sharded = HaloShardedSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device)
+            my_col = sharded.col
+            x = sharded.compact
+            sent, received = sharded.exchange_rows()
+            config["parallelism"] = f"row_shard{world}_halo_alltoall_x"
+            config["halo_rows_rank0"] = {"sent": sent, "received": received}
+        else:
+            block = nodes // world
+            x_block = x[rank * block:(rank + 1) * block].clone()
+            del rowptr, col, value, x
+            torch.cuda.empty_cache()
+            sharded = RowShardedSpmm(my_ptr, my_col, my_val, block, args.feat, dtype, device)
+            x = sharded.gathered[0]  # filled by the all-gather of every step, never by the generator
+            config["parallelism"] = f"row_shard{world}_allgather_x"
     else:
         my_ptr, my_col, my_val = rowptr, col, value
         x_block = None
@@ -237,7 +253,7 @@ def main():
 
     def step():
         if distributed:
-            return sharded([x_block])[0]
+            return sharded(x_block) if args.exchange == "halo" else sharded([x_block])[0]
         return forward(my_ptr, my_col, my_val, x, 0, out_code)[0]
 
     def barrier():
@@ -274,9 +290,11 @@ def main():
             forward(my_ptr, my_col, my_val, x, 0, out_code)
         stop.record()
         barrier()
-        local_ms = torch.tensor([start.elapsed_time(stop)], device=device)
-        dist.all_reduce(local_ms, op=dist.ReduceOp.MAX)
-        resident_ms = float(local_ms.item()) / args.steps
+        local_ms = torch.tensor([start.elapsed_time(stop) / args.steps], device=device)
+        every_ms = torch.empty(world, device=device)
+        dist.all_gather_into_tensor(every_ms, local_ms)
+        resident_ms = float(every_ms.max().item())
+        resident_per_rank = [round(v, 3) for v in every_ms.tolist()]
 
     result = {
         "metric": "spmm_sum_nnz_feat_per_s", "value": nnz * args.feat / (ms_per_step * 1e-3), "unit": "nnz*feat/s",
@@ -288,6 +306,7 @@ def main():
     }
     if resident_ms is not None:
         result["x_resident"] = {"ms_per_step": resident_ms, "value": nnz * args.feat / (resident_ms * 1e-3),
+                                "per_rank_ms": resident_per_rank,
                                 "note": "local SpMM only, X already replicated (no all-gather in the step)"}
 
     if rank == 0:
@@ -445,7 +464,7 @@ def end_to_end_sharded(args, sharded, x_block, nnz, dist, device):
 
     def product(dev):
         sharded.rowptr, sharded.col, sharded.value = dev[0], dev[1], dev[2]
-        return sharded([dev[3]])[0]
+        return sharded(dev[3]) if args.exchange == "halo" else sharded([dev[3]])[0]
 
     def barrier():
         torch.cuda.synchronize()

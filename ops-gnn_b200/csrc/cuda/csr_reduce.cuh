@@ -286,6 +286,21 @@ __device__ __forceinline__ void BulkLoad(uint32_t dst, const void* src, uint32_t
                  : "memory");
 }
 
+// Two ways to fill the ring.  Wide rows (512 bytes and more): one `cp.async.bulk` per gathered row, completion on an
+// mbarrier per stage.  Narrow rows: per-lane 16-byte `cp.async.cg` copies, so one warp instruction moves 32 / lanes
+// per row rows, completion by commit / wait groups.  Measured on an R-MAT graph (64M edges): bulk copies win by 3-4 %
+// at 512-byte and 1-KiB rows, per-lane copies by 5-25 % below that (a bulk copy is issued once per active lane).
+
+__device__ __forceinline__ void AsyncCopy16(uint32_t dst, const void* src)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void AsyncCommit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int PENDING> __device__ __forceinline__ void AsyncWait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
+}
+
 template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK> struct Traits {
     using A = typename AccOf<T>::type;
     static constexpr int kTile = 32 * VEC * NV;
@@ -312,6 +327,7 @@ template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, boo
 __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
 {
     static_assert(!NARROW || (BULK && NV == 1 && !GENERAL), "the narrow layout exists for lean bulk instances only");
+    constexpr bool kRingAsync = NARROW;
     static_assert(NARROW || (BULK ? kBulkStageBytes / (32 * VEC * NV * static_cast<int>(sizeof(T))) : 16) <= 16,
                   "the slot dispatch below enumerates sixteen slots");
     using TR = Traits<T, O, PtrT, ColT, VEC, NV, RK>;
@@ -429,7 +445,7 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
                                                       ((GENERAL && BULK) ? warp * kBulkStages * kBulkWeightBytes : 0));
     const uint32_t weight_addr = (GENERAL && BULK) ? SharedAddress(weight_ring) : 0u;
     const uint32_t weight_row_bytes = static_cast<uint32_t>(p.val_width * static_cast<int64_t>(sizeof(T)));
-    if constexpr (BULK) {
+    if constexpr (BULK && !kRingAsync) {
         if (lane == 0) {
 #pragma unroll
             for (int st = 0; st < kBulkStages; ++st) {
@@ -604,6 +620,21 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
         static_cast<uint32_t>((K - kbase < TILE ? K - kbase : static_cast<int64_t>(TILE)) * static_cast<int64_t>(sizeof(T)));
     auto issue = [&](int b) {
         const int first = j0 + b * eb;
+        if constexpr (kRingAsync) {
+            // One commit group per batch, empty ones included, so "all but the newest kBulkStages - 1 groups" always
+            // means "every batch up to the one about to be consumed".
+            const int n = (first >= j1) ? 0 : ((j1 - first < eb) ? j1 - first : eb);
+            const uint32_t stage_addr = ring_addr + static_cast<uint32_t>((b % kBulkStages) * kBulkStageBytes);
+            for (int rr = 0; rr < n; rr += groups) {
+                const int r = rr + grp;
+                if (r < n) {
+                    AsyncCopy16(stage_addr + static_cast<uint32_t>(r * row_bytes + lane_in * 16),
+                                lane_base[0] + static_cast<int64_t>(s_col[first + r]) * K32);
+                }
+            }
+            AsyncCommit();
+            return;
+        }
         if (first >= j1) {
             return;
         }
@@ -647,7 +678,12 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
         const int nb = (j1 - j < eb) ? j1 - j : eb;
         Pack<T, VEC> x[BULK ? 1 : EB][NV];
         const unsigned char* stage = ring + (batch_id % kBulkStages) * kBulkStageBytes;
-        if constexpr (BULK) {
+        if constexpr (BULK && kRingAsync) {
+            if (nb > 0) {
+                AsyncWait<kBulkStages - 1>();
+                __syncwarp();  // a row is read by other lanes than the ones that copied it
+            }
+        } else if constexpr (BULK) {
             if (nb > 0) {
                 const uint32_t bar = bar_addr + (batch_id % kBulkStages) * 8;
                 const uint32_t parity = static_cast<uint32_t>(batch_id / kBulkStages) & 1u;
@@ -816,7 +852,9 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
             }
         }
     }
-    if constexpr (BULK) {
+    if constexpr (BULK && kRingAsync) {
+        AsyncWait<0>();  // nothing is outstanding by construction; the ring is about to hold the carries
+    } else if constexpr (BULK) {
         if (stalled) {
             // Give copies still in flight a bounded chance to land before the block's shared memory is released.
             for (int b = batch_id; b < batch_id + kBulkStages; ++b) {

@@ -117,3 +117,79 @@ class RowShardedSpmm:
             outputs.append(self.local_spmm(self.rowptr, self.col, self.value, self.gathered[c]))
         self.side_stream.wait_stream(main)
         return outputs
+
+
+class HaloShardedSpmm:
+    """One rank's share of ``out = A @ X`` that moves only the rows of ``X`` its shard references.
+
+    ``A`` is cut into the row ranges ``bounds`` (one per rank) and ``X`` is owned by the same ranges, the layout a
+    stack of GNN layers produces: a rank's output rows are its block of the next layer's input.  An all-gather
+    would hand every rank all of ``X``; a shard of a sparse graph reads far fewer distinct rows than that.  Here the
+    set-up (once per graph) finds the distinct columns of the shard, tells every owner which of its rows are wanted,
+    and relabels the shard's columns into a compact buffer ``[own rows | halo rows grouped by owner]``.  A step is
+    then: pack the wanted rows per peer, one all-to-all with uneven splits that lands the halo in this GPU's memory,
+    and the local SpMM over the compact buffer.  No kernel reads peer memory.
+
+    ``gather_rows(x, index)`` packs rows (default: the CSR engine run as a gather, a unit pointer array with the
+    wanted rows as columns); ``local_spmm`` as in :class:`RowShardedSpmm`.
+    """
+
+    def __init__(self, rowptr, col, value, bounds: Sequence[int], feat: int, dtype, device, group=None,
+                 local_spmm: Optional[Callable] = None, gather_rows: Optional[Callable] = None):
+        import torch.distributed as dist
+
+        self.dist, self.group = dist, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if len(bounds) != self.world + 1:
+            raise ValueError("bounds must hold one row range per rank")
+        self.bounds = [int(b) for b in bounds]
+        self.own_first, own_last = self.bounds[self.rank], self.bounds[self.rank + 1]
+        self.own_rows = own_last - self.own_first
+        edges = torch.tensor(self.bounds, dtype=col.dtype, device=device)
+
+        # distinct columns of the shard, split into the part this rank owns and the halo, grouped by owner
+        needed = torch.unique(col)
+        owner = torch.searchsorted(edges, needed, right=True) - 1
+        remote = needed[owner != self.rank]                      # sorted, hence already grouped by owner
+        want_counts = torch.bincount(owner[owner != self.rank], minlength=self.world)
+        give_counts = torch.empty_like(want_counts)
+        dist.all_to_all_single(give_counts, want_counts, group=group)
+        self.want_splits = [int(c) for c in want_counts.tolist()]
+        self.give_splits = [int(c) for c in give_counts.tolist()]
+        wanted_of_me = torch.empty(sum(self.give_splits), dtype=col.dtype, device=device)
+        dist.all_to_all_single(wanted_of_me, remote.contiguous(), self.give_splits, self.want_splits, group=group)
+        self.send_rows = (wanted_of_me - self.own_first).contiguous()   # offsets into this rank's block, per peer
+        if self.send_rows.numel() and (int(self.send_rows.min()) < 0 or int(self.send_rows.max()) >= self.own_rows):
+            raise RuntimeError("a peer asked for rows outside this rank's block: shard bounds disagree between ranks")
+        self.halo_rows = int(remote.numel())
+
+        # compact column ids: own rows first, then the halo in the order it is received
+        is_own = (col >= self.own_first) & (col < own_last)
+        compact = torch.where(is_own, col - self.own_first, self.own_rows + torch.searchsorted(remote, col))
+        self.rowptr, self.col, self.value = rowptr, compact.contiguous(), value
+        self.compact = torch.empty((self.own_rows + self.halo_rows, feat), dtype=dtype, device=device)
+        self.own_block = self.compact[:self.own_rows]            # the caller may produce its block here directly
+        self.halo = self.compact[self.own_rows:]
+        self.unit_ptr = torch.arange(self.send_rows.numel() + 1, dtype=col.dtype, device=device)
+        if local_spmm is None or gather_rows is None:
+            from .torch_sparse_spmm import _native
+
+            out_code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}[dtype]
+            if local_spmm is None:
+                local_spmm = lambda ptr, c, v, x: _native.forward(ptr, c, v, x, 0, out_code)[0]  # noqa: E731
+            if gather_rows is None:
+                gather_rows = lambda x, index: _native.forward(self.unit_ptr, index, None, x, 0, out_code)[0]  # noqa: E731
+        self.local_spmm, self.gather_rows = local_spmm, gather_rows
+
+    def exchange_rows(self) -> Tuple[int, int]:
+        """(rows this rank sends, rows it receives) per step."""
+        return int(self.send_rows.numel()), self.halo_rows
+
+    def __call__(self, x_block: torch.Tensor) -> torch.Tensor:
+        if x_block.data_ptr() != self.own_block.data_ptr():
+            self.own_block.copy_(x_block)
+        if self.world > 1:
+            packed = self.gather_rows(self.own_block, self.send_rows) if self.send_rows.numel() else \
+                self.own_block.new_empty((0, self.own_block.size(1)))
+            self.dist.all_to_all_single(self.halo, packed, self.want_splits, self.give_splits, group=self.group)
+        return self.local_spmm(self.rowptr, self.col, self.value, self.compact)
