@@ -19,8 +19,12 @@ The line printed by rank 0 carries
               threads,
   clocks      SM clock and throttle reasons sampled by nvidia-smi during the timed region.
 
-N > 1 (torchrun, one rank per GPU): output rows are split into nnz-balanced contiguous ranges, every rank owns an
-equal row block of X and each step all-gathers X over NCCL before the local SpMM (strong scaling: the graph is fixed).
+N > 1 (torchrun, one rank per GPU; strong scaling: the graph is fixed): output rows are split into contiguous ranges
+of equal work (edges + 4 per row).  `--exchange halo` (default): X is owned by the same row ranges and each step moves
+only the rows of X a shard references (pack, one NCCL all-to-all with uneven splits, local SpMM over the compact
+buffer).  `--exchange allgather`: every rank owns an equal row block of X and each step all-gathers all of X.  The
+`x_resident` record times the local SpMM alone.  The host-buffer leg at N > 1 uses the all-gather form, with shard
+bounds chosen for PCIe (a row weighs 50 edges there).
 `--impl reference` times the reference's CPU algorithm (the oracle port) on the host cores for the same metric.
 """
 import argparse
@@ -165,9 +169,10 @@ def parse():
     parser.add_argument("--edge-factor", type=int, default=16)
     parser.add_argument("--feat", type=int, default=256)
     parser.add_argument("--dtype", default="fp32", choices=("fp32", "bf16"))
-    parser.add_argument("--exchange", default="allgather", choices=("allgather", "halo"),
+    parser.add_argument("--exchange", default="halo", choices=("allgather", "halo"),
                         help="N > 1: all-gather of X, or an all-to-all of only the rows each shard references")
     parser.add_argument("--row-cost", type=float, default=4.0, help="N > 1: cost of one output row in edges (shard balance)")
+    parser.add_argument("--e2e-row-cost", type=float, default=50.0, help="N > 1: the same for the host-buffer leg")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     return parser.parse_args()
@@ -227,6 +232,16 @@ def main():
         bounds = balanced_row_bounds(rowptr, world, row_cost=args.row_cost)
         my_ptr, my_col, my_val = shard_csr(rowptr, col, value, bounds[rank], bounds[rank + 1])
         config["shard_rows"] = bounds[rank + 1] - bounds[rank]
+        host_shard = None
+        if not args.no_e2e:
+            # The host-buffer leg is bound by PCIe, where a row (1 KiB up as X, 1 KiB down as output) weighs as much
+            # as ~50 edges (20 bytes up each): it gets its own shard bounds and equal blocks of X.
+            e2e_bounds = balanced_row_bounds(rowptr, world, row_cost=args.e2e_row_cost)
+            block = nodes // world
+            pieces = shard_csr(rowptr, col, value, e2e_bounds[rank], e2e_bounds[rank + 1])
+            host_shard = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
+                          for t in (*pieces, x[rank * block:(rank + 1) * block])]
+            del pieces
         if args.exchange == "halo":
             # X is owned by the same row ranges as the output (a layer's output rows are the next layer's input)
             x_block = x[bounds[rank]:bounds[rank + 1]].clone()
@@ -335,7 +350,7 @@ def main():
     torch.cuda.empty_cache()
     if not args.no_e2e:
         if distributed:
-            result["e2e"] = end_to_end_sharded(args, sharded, x_block, nnz, dist, device)
+            result["e2e"] = end_to_end_sharded(args, host_shard, nnz, dist, device, world)
         else:
             result["e2e"], host_inputs = end_to_end(args, csr_spmm, rowptr, col, value, x, nnz)
 
@@ -452,19 +467,21 @@ def end_to_end(args, csr_spmm, rowptr, col, value, x, nnz):
             "result_checksum": checksum}, pinned
 
 
-def end_to_end_sharded(args, sharded, x_block, nnz, dist, device):
-    """N > 1: every rank uploads its CSR slice and its block of X, runs the sharded step, downloads its output rows."""
-    inputs = (sharded.rowptr, sharded.col, sharded.value, x_block)
-    pinned = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in inputs]
-    for host, dev in zip(pinned, inputs):
-        host.copy_(dev)
-    rows = sharded.rowptr.numel() - 1
-    out_host = torch.empty((rows, args.feat), dtype=x_block.dtype, pin_memory=True)
-    saved = (sharded.rowptr, sharded.col, sharded.value)
+def end_to_end_sharded(args, pinned, nnz, dist, device, world):
+    """N > 1: every rank uploads its CSR slice and its block of X, runs the sharded step (all-gather of X + local
+    SpMM through `ops_gnn.distributed.RowShardedSpmm`) and downloads its output rows.  `pinned` holds the rank's
+    (rowptr, col, value, block of X) in pinned host memory."""
+    from ops_gnn.distributed import RowShardedSpmm
+
+    like = [torch.empty(t.shape, dtype=t.dtype, device=device) for t in pinned]
+    rows = pinned[0].numel() - 1
+    block_rows, dtype = pinned[3].size(0), pinned[3].dtype
+    out_host = torch.empty((rows, args.feat), dtype=dtype, pin_memory=True)
+    sharded = RowShardedSpmm(None, None, None, block_rows, args.feat, dtype, device)
 
     def product(dev):
         sharded.rowptr, sharded.col, sharded.value = dev[0], dev[1], dev[2]
-        return sharded(dev[3]) if args.exchange == "halo" else sharded([dev[3]])[0]
+        return sharded([dev[3]])[0]
 
     def barrier():
         torch.cuda.synchronize()
@@ -472,18 +489,18 @@ def end_to_end_sharded(args, sharded, x_block, nnz, dist, device):
         torch.cuda.synchronize()
 
     steps = max(3, min(args.steps, 5))
-    local_ms = run_pipelined(pinned, inputs, product, out_host, steps, barrier)
-    sharded.rowptr, sharded.col, sharded.value = saved
+    local_ms = run_pipelined(pinned, like, product, out_host, steps, barrier)
+    del like
     elapsed = torch.tensor([local_ms * steps], device=device)
-    in_bytes = torch.tensor([sum(t.numel() * t.element_size() for t in inputs)], device=device)
-    out_bytes = torch.tensor([rows * args.feat * x_block.element_size()], device=device)
+    in_bytes = torch.tensor([sum(t.numel() * t.element_size() for t in pinned)], device=device)
+    out_bytes = torch.tensor([rows * args.feat * out_host.element_size()], device=device)
     dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
     dist.all_reduce(in_bytes)
     dist.all_reduce(out_bytes)
     ms = float(elapsed.item()) / steps
     return {"value": nnz * args.feat / (ms * 1e-3), "unit": "nnz*feat/s", "ms_per_step": ms, "steps": steps,
             "h2d_bytes_per_step": int(in_bytes.item()), "d2h_bytes_per_step": int(out_bytes.item()),
-            "api": "ops_gnn.distributed.RowShardedSpmm",
+            "api": "ops_gnn.distributed.RowShardedSpmm", "shard_row_cost": args.e2e_row_cost, "rows_rank0": rows,
             "overlap": "upload of step k+1 runs beside product and download of step k (2 staging sets, 3 streams)",
             "note": "bytes are summed over ranks; time is the max over ranks"}
 

@@ -1029,6 +1029,40 @@ __global__ void __launch_bounds__(kThreads) FixupKernel(const Params p)
         }
     }
     const int64_t width = p.batches * K;
+    // Four features per lane when one batch, float accumulators and aligned rows allow it (the SpMM / segment sums):
+    // the loop is a chain of dependent loads, so fewer and wider steps are what shortens it.
+    if constexpr ((RK == kSum || RK == kLogSumExp) && std::is_same<A, float>::value && sizeof(O) >= 2) {
+        if (p.batches == 1 && K % 4 == 0 && p.carry_stride % 4 == 0 &&
+            ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(carry_val)) & 15) == 0) {
+            O* out = static_cast<O*>(p.out);
+            for (int64_t k = static_cast<int64_t>(lane) * 4; k < K; k += 128) {
+                // tiles are padded to `tile` features inside a carry row; K % 4 == 0 keeps a vector inside one tile
+                const int64_t f = (k / tile) * tile + k % tile;
+                float run[4];
+                Unpack<float, float, 4>(LoadPlain<float, 4>(carry_val + b * p.carry_stride + f), run);
+                for (int64_t n = b + 1; n < p.num_cta && p.carry_row[n] == row; ++n) {
+                    float more[4];
+                    Unpack<float, float, 4>(LoadPlain<float, 4>(carry_val + n * p.carry_stride + f), more);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        run[c] = RK == kSum ? run[c] + more[c] : LogAddExp(run[c], more[c]);
+                    }
+                }
+                float old[4];
+                Unpack<float, O, 4>(LoadPlain<O, 4>(out + row * K + k), old);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    if constexpr (RK == kSum) {
+                        old[c] = (divide ? run[c] / scale : run[c]) + old[c];
+                    } else {
+                        old[c] = LogAddExp(run[c], old[c]);
+                    }
+                }
+                StorePlain<O, 4>(out + row * K + k, Repack<O, float, 4>(old));
+            }
+            return;
+        }
+    }
     for (int64_t x = lane; x < width; x += 32) {
         const int64_t batch = x / K;
         const int64_t k = x - batch * K;
