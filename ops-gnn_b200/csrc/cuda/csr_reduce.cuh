@@ -799,7 +799,53 @@ __global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
             }                                                      \
             consume(std::integral_constant<int, N>{});             \
         }
-            if constexpr (NARROW) {
+            if constexpr (RK == kLogSumExp && BULK) {
+                // The run sits in shared memory, so it is read twice: once for the maximum of the run, once for the
+                // sum of exponentials against the updated maximum.  One exponential and no branch per element; the
+                // running sum is rescaled once per run.  fmaxf drops NaN, which then enters the sum as exp(NaN).
+                A run_max[ELEMS];
+#pragma unroll
+                for (int q = 0; q < ELEMS; ++q) {
+                    run_max[q] = -INFINITY;
+                }
+                for (int tt = t_begin; tt < t_end; tt += groups) {
+                    if (tt + grp < t_end) {
+#pragma unroll
+                        for (int v = 0; v < NV; ++v) {
+                            A xs[VEC];
+                            Unpack<A, T, VEC>(LoadPlain<T, VEC>(reinterpret_cast<const T*>(stage + (tt + grp) * row_bytes) +
+                                                                (v * 32 + lane_in) * VEC), xs);
+#pragma unroll
+                            for (int c = 0; c < VEC; ++c) {
+                                run_max[v * VEC + c] = fmaxf(run_max[v * VEC + c], xs[c]);
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int q = 0; q < ELEMS; ++q) {
+                    const A top = fmaxf(acc[q], run_max[q]);
+                    if (top != acc[q]) {  // never taken for equal infinities, so no inf - inf
+                        aux[q] *= __expf(acc[q] - top);
+                        acc[q] = top;
+                    }
+                }
+                for (int tt = t_begin; tt < t_end; tt += groups) {
+                    if (tt + grp < t_end) {
+#pragma unroll
+                        for (int v = 0; v < NV; ++v) {
+                            A xs[VEC];
+                            Unpack<A, T, VEC>(LoadPlain<T, VEC>(reinterpret_cast<const T*>(stage + (tt + grp) * row_bytes) +
+                                                                (v * 32 + lane_in) * VEC), xs);
+#pragma unroll
+                            for (int c = 0; c < VEC; ++c) {
+                                const int q = v * VEC + c;
+                                aux[q] += __expf(xs[c] == acc[q] ? A(0) : xs[c] - acc[q]);
+                            }
+                        }
+                    }
+                }
+            } else if constexpr (NARROW) {
                 for (int tt = t_begin; tt < t_end; tt += groups) {
                     if (tt + grp < t_end) {
                         consume(tt + grp);

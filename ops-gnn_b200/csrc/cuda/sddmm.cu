@@ -10,6 +10,8 @@
 // re-read from L1 across the row's edges; rows selected by the column are the HBM-bound gather.
 //
 // Algorithmic bytes per launch (dot): nnz*(sizeof(index) + F*sizeof(T) + sizeof(T)) + rows*(sizeof(index) + F*sizeof(T)).
+#include <utility>
+
 #include "common.cuh"
 
 namespace opsgnn {
@@ -204,6 +206,153 @@ __global__ void __launch_bounds__(kThreads) SddmmKernel(const Params p)
     }
 }
 
+// ---- dot product, the hot SDDMM form ---------------------------------------------------------------------------------
+// `lpe` lanes share an edge and every lane owns NVL 16-byte vectors of both operand rows, so a 64-float row is four
+// lanes x four vectors: eight edges per warp instruction and two shuffle steps per dot instead of four.  Each lane
+// group walks consecutive edges, and the operand selected by `lhs` is kept in registers until its row id changes:
+// with lhs gathered by the CSR row (the caller swaps the operands when only rhs is) it is loaded once per row, not
+// once per edge.  Row ids are staged as 32-bit numbers; addresses are one 32 x 32 -> 64 multiply-add.
+template <class T, class IndexT, int VEC, int NVL>
+__global__ void __launch_bounds__(kThreads) SddmmDotKernel(const Params p)
+{
+    __shared__ int s_a[kEdgesPerCta];
+    __shared__ int s_b[kEdgesPerCta];
+    __shared__ float s_dot[kEdgesPerCta];
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int64_t cta = blockIdx.x;
+    const int64_t e0 = cta * kEdgesPerCta;
+    const int count = static_cast<int>((p.nnz - e0 < kEdgesPerCta) ? p.nnz - e0 : kEdgesPerCta);
+    const IndexT* __restrict__ ptr = static_cast<const IndexT*>(p.indptr);
+    const IndexT* __restrict__ col = static_cast<const IndexT*>(p.indices);
+    const int F32 = static_cast<int>(p.feat);
+    const bool need_row = p.lhs_target == OPSGNN_TARGET_ROW || p.rhs_target == OPSGNN_TARGET_ROW;
+    const bool need_col = p.lhs_target == OPSGNN_TARGET_COL || p.rhs_target == OPSGNN_TARGET_COL;
+
+    const int64_t row_lo = need_row ? p.plan[cta] : 0;
+    const int64_t row_hi = need_row ? p.plan[cta + 1] : 0;
+    for (int j = tid; j < count; j += kThreads) {
+        const int64_t e = e0 + j;
+        const int64_t r = need_row ? RowOf(ptr, row_lo, row_hi, e) : 0;
+        const int64_t c = need_col ? static_cast<int64_t>(LoadStream(col + e)) : 0;
+        auto pick = [&](int target, int64_t bound) {
+            int64_t v = target == OPSGNN_TARGET_ROW ? r : (target == OPSGNN_TARGET_EDGE ? e : c);
+            v = v < 0 ? 0 : (v >= bound ? bound - 1 : v);  // validated upstream; never fault on a bad index
+            return static_cast<int>(v);                   // operand rows stay below 2^31 (checked by the launcher)
+        };
+        s_a[j] = pick(p.lhs_target, p.lhs_rows);
+        s_b[j] = pick(p.rhs_target, p.rhs_rows);
+    }
+    __syncthreads();
+
+    const int lpe = p.group;
+    const int groups = 32 / lpe;
+    const int g = lane / lpe;
+    const int gl = lane - g * lpe;
+    const int per_group = kEdgesPerWarp / groups;
+    const int first = warp * kEdgesPerWarp + g * per_group;
+    const T* __restrict__ a_base = static_cast<const T*>(p.lhs) + gl * VEC;
+    const T* __restrict__ b_base = static_cast<const T*>(p.rhs) + gl * VEC;
+    const int step = lpe * VEC;  // elements between a lane's consecutive vectors
+
+    float fa[NVL][VEC];
+    int held = -1;  // row id whose lhs fragment sits in fa
+    auto hold = [&](int id) {
+        if (id != held) {
+            const T* row = a_base + static_cast<int64_t>(id) * F32;
+#pragma unroll
+            for (int k = 0; k < NVL; ++k) {
+                Unpack<float, T, VEC>(LoadGather<T, VEC>(row + k * step), fa[k]);
+            }
+            held = id;
+        }
+    };
+    auto dot = [&](const Pack<T, VEC> (&b)[NVL]) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int k = 0; k < NVL; ++k) {
+            float fb[VEC];
+            Unpack<float, T, VEC>(b[k], fb);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                sum += fa[k][i] * fb[i];
+            }
+        }
+        return sum;
+    };
+
+    for (int t = 0; t < per_group; t += 2) {
+        const int j0 = first + t;
+        const int j1 = j0 + 1;
+        const bool live0 = j0 < count;
+        const bool live1 = t + 1 < per_group && j1 < count;
+        Pack<T, VEC> b0[NVL], b1[NVL];
+        if (live0) {
+            const T* row = b_base + static_cast<int64_t>(s_b[j0]) * F32;
+#pragma unroll
+            for (int k = 0; k < NVL; ++k) {
+                b0[k] = LoadGather<T, VEC>(row + k * step);
+            }
+        }
+        if (live1) {
+            const T* row = b_base + static_cast<int64_t>(s_b[j1]) * F32;
+#pragma unroll
+            for (int k = 0; k < NVL; ++k) {
+                b1[k] = LoadGather<T, VEC>(row + k * step);
+            }
+        }
+        float d0 = 0.0f, d1 = 0.0f;
+        if (live0) {
+            hold(s_a[j0]);
+            d0 = dot(b0);
+        }
+        if (live1) {
+            hold(s_a[j1]);
+            d1 = dot(b1);
+        }
+        for (int offset = lpe >> 1; offset > 0; offset >>= 1) {  // offsets below lpe stay inside the lane group
+            d0 += __shfl_xor_sync(0xffffffffu, d0, offset, 32);
+            d1 += __shfl_xor_sync(0xffffffffu, d1, offset, 32);
+        }
+        if (gl == 0) {
+            if (live0) {
+                s_dot[j0] = d0;
+            }
+            if (live1) {
+                s_dot[j1] = d1;
+            }
+        }
+    }
+    __syncwarp();
+    T* __restrict__ out = static_cast<T*>(p.out);
+    const int w0 = warp * kEdgesPerWarp;
+    for (int j = w0 + lane; j < w0 + kEdgesPerWarp && j < count; j += 32) {
+        out[e0 + j] = Narrow<T, float>(s_dot[j]);
+    }
+}
+
+// Vectors per lane for the dot kernel: the widest of 4 / 2 / 1 (at most 16 elements of fp32, 16 of a 16-bit type per
+// operand) that leaves a power-of-two number of lanes per edge, at most 32; 0 when the width does not fit.
+template <class T> inline int DotVectorsPerLane(int64_t feat)
+{
+    constexpr int kVec = 16 / sizeof(T);
+    if (feat % kVec != 0) {
+        return 0;
+    }
+    const int64_t vectors = feat / kVec;
+    for (int nvl = sizeof(T) == 4 ? 4 : 2; nvl >= 1; nvl >>= 1) {
+        if (vectors % nvl == 0) {
+            const int64_t lanes = vectors / nvl;
+            if (lanes <= 32 && (lanes & (lanes - 1)) == 0) {
+                return nvl;
+            }
+        }
+    }
+    return 0;
+}
+
 template <class T, class IndexT, int VEC> int LaunchTyped(const Params& p, cudaStream_t stream)
 {
     const unsigned grid = static_cast<unsigned>(p.num_cta);
@@ -220,6 +369,28 @@ template <class T, class IndexT> int LaunchVec(Params p, cudaStream_t stream)
     constexpr int kVec = 16 / sizeof(T);
     const bool vector_ok = p.feat % kVec == 0 && (p.lhs == nullptr || Aligned(p.lhs, 16)) &&
                            (p.rhs == nullptr || Aligned(p.rhs, 16)) && (p.op == OPSGNN_SDDMM_DOT || Aligned(p.out, 16));
+    if (vector_ok && p.op == OPSGNN_SDDMM_DOT && p.lhs_rows <= 2147483647LL && p.rhs_rows <= 2147483647LL &&
+        p.feat <= 2147483647LL) {
+        const int nvl = DotVectorsPerLane<T>(p.feat);
+        if (nvl > 0) {
+            if (p.lhs_target != OPSGNN_TARGET_ROW && p.rhs_target == OPSGNN_TARGET_ROW) {
+                // a dot product commutes: keep the operand gathered by the CSR row in the cached position
+                std::swap(p.lhs, p.rhs);
+                std::swap(p.lhs_rows, p.rhs_rows);
+                std::swap(p.lhs_target, p.rhs_target);
+            }
+            p.group = static_cast<int>(p.feat / kVec / nvl);
+            const unsigned grid = static_cast<unsigned>(p.num_cta);
+            if (nvl == 4) {
+                SddmmDotKernel<T, IndexT, kVec, 4><<<grid, kThreads, 0, stream>>>(p);
+            } else if (nvl == 2) {
+                SddmmDotKernel<T, IndexT, kVec, 2><<<grid, kThreads, 0, stream>>>(p);
+            } else {
+                SddmmDotKernel<T, IndexT, kVec, 1><<<grid, kThreads, 0, stream>>>(p);
+            }
+            return LaunchStatus();
+        }
+    }
     const int vec = vector_ok ? kVec : 1;
     int group = 1;
     while (group < 32 && static_cast<int64_t>(group) * vec < p.feat) {
