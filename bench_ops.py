@@ -11,7 +11,7 @@ through the public `ops_gnn` API with inputs resident in HBM and prints ONE JSON
 
 Every launch is bracketed by its own pair of CUDA events on the current stream (`--warm` untimed calls first); the
 working sets are larger than L2 (config 2: 512 MiB of src; config 3: 16 GB of gathers), so no flush is needed.  The
-algorithmic bytes are the formulas of the design notes (every gathered row counted as a DRAM read).  The CPU
+algorithmic bytes are written beside every call below (every gathered row counted as a DRAM read).  The CPU
 baseline is the oracle of the same operator on a bounded sample with all host threads.  All inputs are seeded
 synthetic tensors (seed = 20261125 + config number).
 """

@@ -1,7 +1,7 @@
 """Generate the golden fixtures of this directory by RUNNING THE REFERENCE'S OWN golden functions.
 
-Run it where the reference checkout exists (``python tests/golden/make_fixtures.py [/path/to/ops-gnn]``, default
-``/root/reference``).  For every operator on the sparse message-passing path it loads the reference's ``golden.py``
+Run it where the reference checkout exists: ``python tests/golden/make_fixtures.py /path/to/ops-gnn``.  For every
+operator on the sparse message-passing path it loads the reference's ``golden.py``
 (or ``python/ops_gnn/scatter.py`` for the ordered scatter reference) with ``runpy``, feeds it small seeded inputs that
 cover the edge cases the reference tests name (empty rows and segments, hub rows, NaN / +-inf, ties, batched pointers,
 caller-provided outputs, every dtype) and stores inputs and outputs in ``<op>.pt``.  The committed ``.pt`` files are what
@@ -14,7 +14,9 @@ import sys
 
 import torch
 
-REFERENCE = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) != 2:
+    raise SystemExit("usage: python tests/golden/make_fixtures.py /path/to/ops-gnn")
+REFERENCE = sys.argv[1]
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
