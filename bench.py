@@ -317,7 +317,8 @@ def main():
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32" if elem == 4 else "bf16",
         "data": "synthetic", "config": config, "clocks": clocks,
         # ReduceKernel + FixupKernel per step on every rank (the plan is cached after warm-up); NCCL's kernels not counted
-        "gpu_launches": args.steps * 2 * world,
+        # (the halo step adds the pack gather, again ReduceKernel + FixupKernel)
+        "gpu_launches": args.steps * world * (4 if distributed and args.exchange == "halo" else 2),
     }
     if resident_ms is not None:
         result["x_resident"] = {"ms_per_step": resident_ms, "value": nnz * args.feat / (resident_ms * 1e-3),
