@@ -1214,34 +1214,47 @@ int LaunchShaped(const Params& p, cudaStream_t stream)
         return bulk_allowed && p.wide == 2 && RK == kSum && vector_ok && p.feat % tile == 0 && Aligned(p.val, 16) &&
                row_bytes % 16 == 0 && rows_per_stage * row_bytes <= kBulkWeightBytes;
     };
-    if constexpr (RK == kSum && sizeof(T) == 4) {
+    constexpr bool kIdentity = std::is_same<ColT, Identity>::value;  // segment calls never carry per-feature weights
+    if constexpr (!kIdentity && RK == kSum && sizeof(T) == 4) {
         if (weighted_bulk(256, kBulkStageBytes / 1024)) {
             return Launch<T, O, PtrT, ColT, 4, 2, RK, true, true>(p, stream);
         }
-    } else if constexpr (RK == kSum && sizeof(T) == 2) {
+    } else if constexpr (!kIdentity && RK == kSum && sizeof(T) == 2) {
         if (weighted_bulk(256, kBulkStageBytes / 512)) {
             return Launch<T, O, PtrT, ColT, 8, 1, RK, true, true>(p, stream);
         }
     }
+    // One lane layout: bulk ring when the tiles cover the width exactly, else register gathers (lean or general).
+    auto shaped = [&](auto vec, auto nv) {
+        constexpr int VEC = decltype(vec)::value;
+        constexpr int NV = decltype(nv)::value;
+        if (bulk && p.feat % (32 * VEC * NV) == 0) {
+            return Launch<T, O, PtrT, ColT, VEC, NV, RK, false, true>(p, stream);
+        }
+        if constexpr (kIdentity) {
+            return Launch<T, O, PtrT, ColT, VEC, NV, RK, false>(p, stream);
+        } else {
+            return lean ? Launch<T, O, PtrT, ColT, VEC, NV, RK, false>(p, stream)
+                        : Launch<T, O, PtrT, ColT, VEC, NV, RK, true>(p, stream);
+        }
+    };
     if constexpr (sizeof(T) == 4) {
         if (vector_ok && p.feat > 128) {
-            return (bulk && p.feat % 256 == 0) ? Launch<T, O, PtrT, ColT, 4, 2, RK, false, true>(p, stream)
-                   : lean ? Launch<T, O, PtrT, ColT, 4, 2, RK, false>(p, stream)
-                          : Launch<T, O, PtrT, ColT, 4, 2, RK, true>(p, stream);
+            return shaped(std::integral_constant<int, 4>{}, std::integral_constant<int, 2>{});
         }
         if (vector_ok) {
-            return (bulk && p.feat % 128 == 0) ? Launch<T, O, PtrT, ColT, 4, 1, RK, false, true>(p, stream)
-                   : lean ? Launch<T, O, PtrT, ColT, 4, 1, RK, false>(p, stream)
-                          : Launch<T, O, PtrT, ColT, 4, 1, RK, true>(p, stream);
+            return shaped(std::integral_constant<int, 4>{}, std::integral_constant<int, 1>{});
         }
     } else if constexpr (sizeof(T) == 2) {
         if (vector_ok) {
-            return (bulk && p.feat % 256 == 0) ? Launch<T, O, PtrT, ColT, 8, 1, RK, false, true>(p, stream)
-                   : lean ? Launch<T, O, PtrT, ColT, 8, 1, RK, false>(p, stream)
-                          : Launch<T, O, PtrT, ColT, 8, 1, RK, true>(p, stream);
+            return shaped(std::integral_constant<int, 8>{}, std::integral_constant<int, 1>{});
         }
     }
-    return Launch<T, O, PtrT, ColT, 1, 4, RK, true>(p, stream);
+    if constexpr (kIdentity) {
+        return Launch<T, O, PtrT, ColT, 1, 4, RK, false>(p, stream);
+    } else {
+        return Launch<T, O, PtrT, ColT, 1, 4, RK, true>(p, stream);
+    }
 }
 
 }  // namespace csr
