@@ -169,8 +169,9 @@ def parse():
     parser.add_argument("--edge-factor", type=int, default=16)
     parser.add_argument("--feat", type=int, default=256)
     parser.add_argument("--dtype", default="fp32", choices=("fp32", "bf16"))
-    parser.add_argument("--exchange", default="halo", choices=("allgather", "halo"),
-                        help="N > 1: all-gather of X, or an all-to-all of only the rows each shard references")
+    parser.add_argument("--exchange", default="halo", choices=("allgather", "halo", "pull"),
+                        help="N > 1: all-gather of X; an all-to-all of only the rows each shard references (halo); or "
+                             "the same rows pulled from the peers' symmetric memory by the gather kernel (pull)")
     parser.add_argument("--row-cost", type=float, default=4.0, help="N > 1: cost of one output row in edges (shard balance)")
     parser.add_argument("--e2e-row-cost", type=float, default=50.0, help="N > 1: the same for the host-buffer leg")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
@@ -242,16 +243,18 @@ def main():
             host_shard = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
                           for t in (*pieces, x[rank * block:(rank + 1) * block])]
             del pieces
-        if args.exchange == "halo":
+        if args.exchange in ("halo", "pull"):
             # X is owned by the same row ranges as the output (a layer's output rows are the next layer's input)
             x_block = x[bounds[rank]:bounds[rank + 1]].clone()
             del rowptr, col, value, x
             torch.cuda.empty_cache()
-            sharded = HaloShardedSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device)
+            sharded = HaloShardedSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device,
+                                      transport="pull" if args.exchange == "pull" else "alltoall")
             my_col = sharded.col
             x = sharded.compact
             sent, received = sharded.exchange_rows()
-            config["parallelism"] = f"row_shard{world}_halo_alltoall_x"
+            config["parallelism"] = (f"row_shard{world}_halo_pull_x" if args.exchange == "pull"
+                                     else f"row_shard{world}_halo_alltoall_x")
             config["halo_rows_rank0"] = {"sent": sent, "received": received}
         else:
             block = nodes // world
@@ -268,7 +271,7 @@ def main():
 
     def step():
         if distributed:
-            return sharded(x_block) if args.exchange == "halo" else sharded([x_block])[0]
+            return sharded([x_block])[0] if args.exchange == "allgather" else sharded(x_block)
         return forward(my_ptr, my_col, my_val, x, 0, out_code)[0]
 
     def barrier():
@@ -317,8 +320,9 @@ def main():
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32" if elem == 4 else "bf16",
         "data": "synthetic", "config": config, "clocks": clocks,
         # ReduceKernel + FixupKernel per step on every rank (the plan is cached after warm-up); NCCL's kernels not counted
-        # (the halo step adds the pack gather, again ReduceKernel + FixupKernel)
-        "gpu_launches": args.steps * world * (4 if distributed and args.exchange == "halo" else 2),
+        # (the halo step adds the pack gather, again ReduceKernel + FixupKernel; the pull step one gather per peer)
+        "gpu_launches": args.steps * world * (2 if not distributed or args.exchange == "allgather"
+                                              else 4 if args.exchange == "halo" else 2 * world),
     }
     if resident_ms is not None:
         result["x_resident"] = {"ms_per_step": resident_ms, "value": nnz * args.feat / (resident_ms * 1e-3),

@@ -13,6 +13,11 @@
 //    loads; each warp then walks its items with warp-uniform control flow: all 32 lanes work on the same edge and
 //    own different features, so a gathered dense row is read with one or two 16-byte loads per lane (a 512-byte
 //    or 1-KiB fully coalesced request per warp) and kEdgeBatch rows are in flight per warp before the first use.
+//  * Instances (template flags of ReduceKernel): BULK keeps the gathered rows of a batch in a per-warp ring in shared
+//    memory instead of registers (bulk copies + mbarriers for rows of 512 bytes and more); NARROW lets several lane
+//    groups share a warp when a row is 16 to 256 bytes (per-lane cp.async copies, partial results merged by shuffles
+//    at row ends); GENERAL adds one weight per feature or per feature group (with BULK: per-group weights ride in the
+//    ring beside the rows).  Everything else (extrema under three tie / NaN rules, online log-sum-exp, mean) is shared.
 //  * A row that ends inside the warp's items is written with streaming 16-byte stores.  Edges of a row whose end
 //    lies in a later warp are a "carry": carries are combined in item order after a block barrier, rows that
 //    end in the same block are patched in place, and at most one carry per block goes to global scratch where

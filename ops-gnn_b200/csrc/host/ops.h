@@ -25,6 +25,7 @@ at::Tensor SpmmMinCsr(const at::Tensor& indptr, const at::Tensor& indices, const
 at::Tensor UnifiedSpmmCsr(const at::Tensor& indptr, const at::Tensor& indices, const at::Tensor& x,
                           const std::string& op, const std::string& reduce, const std::optional<at::Tensor>& out);
 
+at::Tensor GatherRows(const at::Tensor& x, const at::Tensor& index, const at::Tensor& unit_ptr, const at::Tensor& out);
 at::Tensor SpmmWeightedCsr(const at::Tensor& indptr, const at::Tensor& indices, const at::Tensor& x,
                            const at::Tensor& weight, const std::string& reduce);
 

@@ -35,6 +35,9 @@ void BindSpmm(py::module_& m)
           py::arg("reduce") = "sum",
           "CSR SpMM with one edge weight per feature group (fused `mul` message); not part of the reference binding",
           py::call_guard<py::gil_scoped_release>());
+    m.def("gather_rows", &GatherRows, py::arg("x"), py::arg("index"), py::arg("unit_ptr"), py::arg("out"),
+          "out[i] = x[index[i]] through the CSR engine (unit_ptr = 0..n); not part of the reference binding",
+          py::call_guard<py::gil_scoped_release>());
     auto sub = m.def_submodule("torch_sparse_spmm", "torch_sparse SpMM on CUDA");
     sub.def("forward", &TorchSparseSpmmForward, py::arg("ptr"), py::arg("col"), py::arg("value"), py::arg("mat"),
             py::arg("reduce"), py::arg("outtype"), py::call_guard<py::gil_scoped_release>());

@@ -316,6 +316,49 @@ at::Tensor RunCopyLhs(const at::Tensor& indptr, const at::Tensor& indices, const
 
 }  // namespace
 
+// out[i, :] = x[index[i], :]: the CSR engine run as a gather (one source row per output row, `unit_ptr` = 0..n).
+// Used by the sharded SpMM to pack the rows a peer wants and to pull rows into a halo buffer; `x` may be any
+// device-accessible memory (a peer's buffer mapped into this process included).  The planner's plan cache keys on
+// `unit_ptr`, so a caller that keeps one pointer tensor per exchange partner pays for the plan once.
+at::Tensor GatherRows(const at::Tensor& x, const at::Tensor& index, const at::Tensor& unit_ptr, const at::Tensor& out)
+{
+    const char* api = "gather_rows";
+    for (const auto& tensor : {x, index, unit_ptr, out}) {
+        TORCH_CHECK(tensor.defined() && tensor.device().is_cuda(), api, ": tensors must be CUDA tensors");
+        TORCH_CHECK(tensor.device() == out.device(), api, ": tensors must be on the same GPU");
+    }
+    TORCH_CHECK(x.dim() == 2 && out.dim() == 2 && x.is_contiguous() && out.is_contiguous(), api,
+                ": x and out must be contiguous matrices");
+    TORCH_CHECK(x.scalar_type() == out.scalar_type() && x.size(1) == out.size(1), api, ": x and out must agree in dtype and width");
+    TORCH_CHECK(x.scalar_type() == at::kFloat || x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16, api,
+                ": dtype must be float32, float16 or bfloat16");
+    TORCH_CHECK(index.dim() == 1 && unit_ptr.dim() == 1 && index.is_contiguous() && unit_ptr.is_contiguous() &&
+                    (index.scalar_type() == at::kInt || index.scalar_type() == at::kLong) &&
+                    unit_ptr.scalar_type() == index.scalar_type(),
+                api, ": index and unit_ptr must be contiguous int32/int64 vectors of one dtype");
+    const int64_t n = index.numel();
+    TORCH_CHECK(out.size(0) == n && unit_ptr.numel() == n + 1, api, ": out needs one row and unit_ptr one entry more per index");
+    TORCH_CHECK(!out.is_alias_of(x), api, ": out must not alias x");
+    if (n == 0 || x.size(1) == 0) {
+        return out;
+    }
+    TORCH_CHECK(x.size(0) > 0, api, ": x has no rows");
+    c10::cuda::CUDAGuard guard(out.device());
+    CsrReduceCall call;
+    call.ptr = unit_ptr;
+    call.col = index;
+    call.mat = x;
+    call.out = out;
+    call.rows = n;
+    call.src_rows = x.size(0);
+    call.feat = x.size(1);
+    call.nnz = n;
+    call.arg_none = n;
+    call.reduce = OPSGNN_REDUCE_SUM;
+    RunCsrReduce(call, api);
+    return out;
+}
+
 at::Tensor SpmmSumCsr(const at::Tensor& indptr, const at::Tensor& indices, const at::Tensor& x,
                       const std::optional<at::Tensor>& out)
 {

@@ -132,10 +132,18 @@ class HaloShardedSpmm:
 
     ``gather_rows(x, index)`` packs rows (default: the CSR engine run as a gather, a unit pointer array with the
     wanted rows as columns); ``local_spmm`` as in :class:`RowShardedSpmm`.
+
+    ``transport="pull"`` (CUDA only) drops the pack and the all-to-all: the compact buffers live in symmetric memory
+    (``torch.distributed._symmetric_memory``, every peer's buffer mapped into this process), and a step runs the
+    gather kernel once per peer with the PEER's block as its source and this rank's halo slice as its destination,
+    so each wanted row crosses NVLink once, read by plain (non-multicast) loads of the kernel that also writes it into
+    place.  Two stream-ordered NCCL barriers bracket the pulls: blocks are complete before anyone reads them, and
+    nobody's block changes while a peer still reads it.
     """
 
     def __init__(self, rowptr, col, value, bounds: Sequence[int], feat: int, dtype, device, group=None,
-                 local_spmm: Optional[Callable] = None, gather_rows: Optional[Callable] = None):
+                 local_spmm: Optional[Callable] = None, gather_rows: Optional[Callable] = None,
+                 transport: str = "alltoall"):
         import torch.distributed as dist
 
         self.dist, self.group = dist, group
@@ -167,7 +175,14 @@ class HaloShardedSpmm:
         is_own = (col >= self.own_first) & (col < own_last)
         compact = torch.where(is_own, col - self.own_first, self.own_rows + torch.searchsorted(remote, col))
         self.rowptr, self.col, self.value = rowptr, compact.contiguous(), value
-        self.compact = torch.empty((self.own_rows + self.halo_rows, feat), dtype=dtype, device=device)
+        if transport not in ("alltoall", "pull"):
+            raise ValueError("transport must be 'alltoall' or 'pull'")
+        self.transport = transport
+        total_rows = self.own_rows + self.halo_rows
+        if transport == "pull":
+            self._setup_pull(remote, total_rows, feat, dtype, device)
+        else:
+            self.compact = torch.empty((total_rows, feat), dtype=dtype, device=device)
         self.own_block = self.compact[:self.own_rows]            # the caller may produce its block here directly
         self.halo = self.compact[self.own_rows:]
         self.unit_ptr = torch.arange(self.send_rows.numel() + 1, dtype=col.dtype, device=device)
@@ -181,6 +196,40 @@ class HaloShardedSpmm:
                 gather_rows = lambda x, index: _native.forward(self.unit_ptr, index, None, x, 0, out_code)[0]  # noqa: E731
         self.local_spmm, self.gather_rows = local_spmm, gather_rows
 
+    def _setup_pull(self, remote, total_rows, feat, dtype, device) -> None:
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads only, no multicast binding
+        import torch.distributed._symmetric_memory as symm
+
+        from .torch_sparse_spmm import _native
+
+        most = torch.tensor([total_rows], dtype=torch.int64, device=device)
+        self.dist.all_reduce(most, op=self.dist.ReduceOp.MAX, group=self.group)
+        capacity = max(int(most.item()), 1)             # symmetric allocations have one size on every rank
+        buffer = symm.empty((capacity, feat), dtype=dtype, device=device)
+        self._handle = symm.rendezvous(buffer, self.group if self.group is not None else self.dist.group.WORLD)
+        self._buffer = buffer
+        self.compact = buffer[:total_rows]
+        self._pulls = []                                # (peer block, wanted rows inside it, unit pointers, halo slice)
+        offset = 0
+        for peer in range(self.world):
+            count = self.want_splits[peer]
+            if peer == self.rank or count == 0:
+                offset += count if peer != self.rank else 0
+                continue
+            wanted = (remote[offset:offset + count] - self.bounds[peer]).contiguous()
+            block = self._handle.get_buffer(peer, (capacity, feat), dtype)
+            unit = torch.arange(count + 1, dtype=wanted.dtype, device=device)
+            self._pulls.append((peer, block, wanted, unit, self.own_rows + offset, count))
+            offset += count
+        self._pulls.sort(key=lambda item: (item[0] - self.rank) % self.world)  # next rank first: no lockstep on one peer
+        self._gather_into = _native.gather_rows
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def _stream_barrier(self) -> None:
+        self.dist.all_reduce(self._flag, group=self.group)  # ordered on the current stream; no host wait
+
     def exchange_rows(self) -> Tuple[int, int]:
         """(rows this rank sends, rows it receives) per step."""
         return int(self.send_rows.numel()), self.halo_rows
@@ -188,7 +237,12 @@ class HaloShardedSpmm:
     def __call__(self, x_block: torch.Tensor) -> torch.Tensor:
         if x_block.data_ptr() != self.own_block.data_ptr():
             self.own_block.copy_(x_block)
-        if self.world > 1:
+        if self.world > 1 and self.transport == "pull":
+            self._stream_barrier()
+            for _, block, wanted, unit, start, count in self._pulls:
+                self._gather_into(block, wanted, unit, self.compact[start:start + count])
+            self._stream_barrier()
+        elif self.world > 1:
             packed = self.gather_rows(self.own_block, self.send_rows) if self.send_rows.numel() else \
                 self.own_block.new_empty((0, self.own_block.size(1)))
             self.dist.all_to_all_single(self.halo, packed, self.want_splits, self.give_splits, group=self.group)
