@@ -202,7 +202,7 @@ class HaloShardedSpmm:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads only, no multicast binding
         import torch.distributed._symmetric_memory as symm
 
-        from .torch_sparse_spmm import _native
+        from . import _pybind
 
         most = torch.tensor([total_rows], dtype=torch.int64, device=device)
         self.dist.all_reduce(most, op=self.dist.ReduceOp.MAX, group=self.group)
@@ -224,7 +224,7 @@ class HaloShardedSpmm:
             self._pulls.append((peer, block, wanted, unit, self.own_rows + offset, count))
             offset += count
         self._pulls.sort(key=lambda item: (item[0] - self.rank) % self.world)  # next rank first: no lockstep on one peer
-        self._gather_into = _native.gather_rows
+        self._gather_into = _pybind.gather_rows
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
 
     def _stream_barrier(self) -> None:
