@@ -20,9 +20,11 @@ The line printed by rank 0 carries
   clocks      SM clock and throttle reasons sampled by nvidia-smi during the timed region.
 
 N > 1 (torchrun, one rank per GPU; strong scaling: the graph is fixed): output rows are split into contiguous ranges
-of equal work (edges + 4 per row).  `--exchange halo` (default): X is owned by the same row ranges and each step moves
-only the rows of X a shard references (pack, one NCCL all-to-all with uneven splits, local SpMM over the compact
-buffer).  `--exchange allgather`: every rank owns an equal row block of X and each step all-gathers all of X.  The
+of equal work (edges + 6 per row).  X is owned by the same row ranges and each step moves only the rows of X a shard
+references into a compact buffer before the local SpMM: `--exchange pull` (default) runs the gather kernel once per
+peer with the peer's block (symmetric memory) as its source; `--exchange halo` packs the rows and sends them with one
+NCCL all-to-all (also the fallback when symmetric memory cannot be set up).  `--exchange allgather`: every rank owns
+an equal row block of X and each step all-gathers all of X.  The
 `x_resident` record times the local SpMM alone.  The host-buffer leg at N > 1 uses the all-gather form, with shard
 bounds chosen for PCIe (a row weighs 50 edges there).
 `--impl reference` times the reference's CPU algorithm (the oracle port) on the host cores for the same metric.
@@ -169,10 +171,10 @@ def parse():
     parser.add_argument("--edge-factor", type=int, default=16)
     parser.add_argument("--feat", type=int, default=256)
     parser.add_argument("--dtype", default="fp32", choices=("fp32", "bf16"))
-    parser.add_argument("--exchange", default="halo", choices=("allgather", "halo", "pull"),
+    parser.add_argument("--exchange", default="pull", choices=("allgather", "halo", "pull"),
                         help="N > 1: all-gather of X; an all-to-all of only the rows each shard references (halo); or "
                              "the same rows pulled from the peers' symmetric memory by the gather kernel (pull)")
-    parser.add_argument("--row-cost", type=float, default=4.0, help="N > 1: cost of one output row in edges (shard balance)")
+    parser.add_argument("--row-cost", type=float, default=6.0, help="N > 1: cost of one output row in edges (shard balance)")
     parser.add_argument("--e2e-row-cost", type=float, default=50.0, help="N > 1: the same for the host-buffer leg")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
@@ -248,8 +250,22 @@ def main():
             x_block = x[bounds[rank]:bounds[rank + 1]].clone()
             del rowptr, col, value, x
             torch.cuda.empty_cache()
-            sharded = HaloShardedSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device,
-                                      transport="pull" if args.exchange == "pull" else "alltoall")
+            transport = "pull" if args.exchange == "pull" else "alltoall"
+            try:
+                sharded = HaloShardedSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device, transport=transport)
+                failure = None
+            except (RuntimeError, ImportError, AttributeError) as exc:  # symmetric memory unavailable on this box
+                sharded, failure = None, f"{type(exc).__name__}: {exc}"[:200]
+            agreed = torch.tensor([0 if failure else 1], device=device)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if int(agreed.item()) == 0:  # every rank falls back together
+                if transport == "alltoall":
+                    raise RuntimeError(f"sharded SpMM set-up failed: {failure}")
+                sharded = None
+                torch.cuda.empty_cache()
+                sharded = HaloShardedSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device, transport="alltoall")
+                args.exchange = "halo"
+                config["exchange_fallback"] = failure or "symmetric memory set-up failed on another rank"
             my_col = sharded.col
             x = sharded.compact
             sent, received = sharded.exchange_rows()
