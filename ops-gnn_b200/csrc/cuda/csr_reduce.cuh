@@ -258,7 +258,11 @@ constexpr int kBulkSmemBytes = kWarps * kBulkWarpBytes + kWarps * kBulkStages * 
 // weights of the stage's edges are contiguous in memory, so one more bulk copy per stage brings them in.
 constexpr int kBulkWeightBytes = 128;  // per stage: rows per stage x weights per edge x sizeof(T) must fit
 constexpr int kBulkSmemBytesWeighted = kBulkSmemBytes + kWarps * kBulkStages * kBulkWeightBytes;
-constexpr uint32_t kBulkSpinLimit = 1u << 22;  // bounded wait on a stage; past it the kernel flags an error and leaves
+// A failed try_wait may suspend the thread for up to this many nanoseconds (it wakes as soon as the phase completes),
+// so a waiting warp does not burn issue slots polling; the poll count bounds the wait to a few seconds in total, past
+// which the kernel flags an error and leaves.
+constexpr uint32_t kBulkWaitHintNs = 100000u;
+constexpr uint32_t kBulkSpinLimit = 1u << 15;
 
 __device__ __forceinline__ uint32_t SharedAddress(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count)
@@ -275,11 +279,11 @@ __device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity)
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kBulkWaitHintNs)
         : "memory");
     return done != 0;
 }
