@@ -234,7 +234,8 @@ class HaloShardedSpmm:
         """(rows this rank sends, rows it receives) per step."""
         return int(self.send_rows.numel()), self.halo_rows
 
-    def __call__(self, x_block: torch.Tensor) -> torch.Tensor:
+    def exchange(self, x_block: torch.Tensor) -> torch.Tensor:
+        """Bring the rank's block and its halo together; returns the compact ``[own rows | halo rows]`` matrix."""
         if x_block.data_ptr() != self.own_block.data_ptr():
             self.own_block.copy_(x_block)
         if self.world > 1 and self.transport == "pull":
@@ -246,4 +247,32 @@ class HaloShardedSpmm:
             packed = self.gather_rows(self.own_block, self.send_rows) if self.send_rows.numel() else \
                 self.own_block.new_empty((0, self.own_block.size(1)))
             self.dist.all_to_all_single(self.halo, packed, self.want_splits, self.give_splits, group=self.group)
-        return self.local_spmm(self.rowptr, self.col, self.value, self.compact)
+        return self.compact
+
+    def __call__(self, x_block: torch.Tensor) -> torch.Tensor:
+        return self.local_spmm(self.rowptr, self.col, self.value, self.exchange(x_block))
+
+
+class HaloShardedSddmm(HaloShardedSpmm):
+    """One rank's share of ``out[e] = <A[row(e)], B[col(e)]>`` over a row-sharded graph.
+
+    The rows of ``A`` an edge needs are the shard's own rows; the rows of ``B`` are its columns, so ``B`` goes through
+    the same needed-rows exchange as the dense operand of :class:`HaloShardedSpmm` (same ``bounds``, ``transport``
+    and stand-in hooks) and the local SDDMM reads the compact buffer through the relabelled columns.  The result is
+    the rank's slice of the edge values, in the order of its CSR slice.
+    """
+
+    def __init__(self, rowptr, col, bounds: Sequence[int], feat: int, dtype, device, group=None,
+                 local_sddmm: Optional[Callable] = None, gather_rows: Optional[Callable] = None,
+                 transport: str = "alltoall"):
+        super().__init__(rowptr, col, None, bounds, feat, dtype, device, group=group,
+                         local_spmm=(lambda *unused: None) if local_sddmm is not None else None,
+                         gather_rows=gather_rows, transport=transport)
+        if local_sddmm is None:
+            from .sddmm_csr import sddmm_csr
+
+            local_sddmm = lambda ptr, c, lhs, rhs: sddmm_csr(ptr, c, lhs, rhs, "dot", "u", "v")  # noqa: E731
+        self.local_sddmm = local_sddmm
+
+    def __call__(self, lhs_block: torch.Tensor, rhs_block: torch.Tensor) -> torch.Tensor:
+        return self.local_sddmm(self.rowptr, self.col, lhs_block, self.exchange(rhs_block))

@@ -78,7 +78,15 @@ def _halo_worker(rank, world, port, result_dir):
     out = op(x[bounds[rank]:bounds[rank + 1]])
     again = op(op.own_block)                                     # producing the block in place skips the copy
     assert torch.equal(out, again)
-    torch.save({"out": out, "exchange": op.exchange_rows(), "rows": x.size(0), "col": col},
+    from ops_gnn.distributed import HaloShardedSddmm
+    from oracle import sddmm_oracle
+
+    other = torch.randn(x.size(0), 12, generator=torch.Generator().manual_seed(6))
+    edge_op = HaloShardedSddmm(ptr, c, bounds, x.size(1), x.dtype, torch.device("cpu"),
+                               local_sddmm=lambda p_, c_, lhs, rhs: sddmm_oracle(p_, c_, lhs, rhs, "dot", "u", "v"),
+                               gather_rows=lambda block, index: block[index])
+    dots = edge_op(other[bounds[rank]:bounds[rank + 1]], x[bounds[rank]:bounds[rank + 1]])
+    torch.save({"out": out, "exchange": op.exchange_rows(), "rows": x.size(0), "col": col, "dots": dots},
                os.path.join(result_dir, f"halo{rank}.pt"))
     dist.barrier()
     dist.destroy_process_group()
@@ -99,6 +107,11 @@ def test_halo_sharded_spmm_gloo(tmp_path):
     sent = sum(p["exchange"][0] for p in parts)
     received = sum(p["exchange"][1] for p in parts)
     assert sent == received and 0 < received < x.size(0)        # fewer rows move than an all-gather would move
+    from oracle import sddmm_oracle
+
+    other = torch.randn(x.size(0), 12, generator=torch.Generator().manual_seed(6))
+    want_dots = sddmm_oracle(rowptr, col, other, x, "dot", "u", "v")
+    assert torch.allclose(torch.cat([p["dots"] for p in parts]), want_dots, rtol=1e-5, atol=1e-5)
 
 
 def _run(chunks, tmp_path):

@@ -61,6 +61,14 @@ def _worker(rank, world, port, result_dir):
         assert torch.equal(first, second), transport
         results[transport] = first.cpu()
         results[transport + "_exchange"] = op.exchange_rows()
+    from ops_gnn.distributed import HaloShardedSddmm
+
+    left = torch.randn(nodes, 64, generator=torch.Generator().manual_seed(43)).to(device)
+    right = torch.randn(nodes, 64, generator=torch.Generator().manual_seed(44)).to(device)
+    for transport in ("alltoall", "pull"):
+        edge_op = HaloShardedSddmm(ptr, c, bounds, 64, left.dtype, device, transport=transport)
+        results["dots_" + transport] = edge_op(left[bounds[rank]:bounds[rank + 1]].contiguous(),
+                                               right[bounds[rank]:bounds[rank + 1]].contiguous()).cpu()
     torch.cuda.synchronize()
     torch.save(results, os.path.join(result_dir, f"rank{rank}.pt"))
     dist.barrier()
@@ -87,6 +95,14 @@ def test_sharded_spmm_two_gpus(tmp_path):
         # row's own edges, but rows may straddle different block boundaries: compare within the fp32 sum tolerance
         scale = want.abs().max().item()
         assert float((got - want).abs().max()) <= 2e-5 * max(scale, 1.0), form
+    import ops_gnn
+
+    left = torch.randn(x.size(0), 64, generator=torch.Generator().manual_seed(43)).to("cuda:0")
+    right = torch.randn(x.size(0), 64, generator=torch.Generator().manual_seed(44)).to("cuda:0")
+    want_dots = ops_gnn.sddmm_csr(rowptr, col, left, right, "dot", "u", "v").cpu()
+    for transport in ("alltoall", "pull"):
+        got_dots = torch.cat([p["dots_" + transport] for p in parts])
+        assert torch.equal(got_dots, want_dots), "sharded SDDMM, " + transport  # a dot product has one summation order
     sent = sum(p["alltoall_exchange"][0] for p in parts)
     received = sum(p["alltoall_exchange"][1] for p in parts)
     assert sent == received and 0 < received < x.size(0)
