@@ -264,15 +264,46 @@ class HaloShardedSddmm(HaloShardedSpmm):
 
     def __init__(self, rowptr, col, bounds: Sequence[int], feat: int, dtype, device, group=None,
                  local_sddmm: Optional[Callable] = None, gather_rows: Optional[Callable] = None,
-                 transport: str = "alltoall"):
+                 transport: str = "alltoall", op: str = "dot"):
         super().__init__(rowptr, col, None, bounds, feat, dtype, device, group=group,
                          local_spmm=(lambda *unused: None) if local_sddmm is not None else None,
                          gather_rows=gather_rows, transport=transport)
         if local_sddmm is None:
             from .sddmm_csr import sddmm_csr
 
-            local_sddmm = lambda ptr, c, lhs, rhs: sddmm_csr(ptr, c, lhs, rhs, "dot", "u", "v")  # noqa: E731
+            local_sddmm = lambda ptr, c, lhs, rhs: sddmm_csr(ptr, c, lhs, rhs, op, "u", "v")  # noqa: E731
         self.local_sddmm = local_sddmm
 
     def __call__(self, lhs_block: torch.Tensor, rhs_block: torch.Tensor) -> torch.Tensor:
         return self.local_sddmm(self.rowptr, self.col, lhs_block, self.exchange(rhs_block))
+
+
+
+class ShardedGatLayer:
+    """A GAT-style attention layer over a row-sharded graph, composed from the sharded operators.
+
+    Per head ``h``: ``logit[e, h] = left[row(e), h] + right[col(e), h]``, LeakyReLU, softmax over the edges of each
+    destination row, ``out[r, h, :] = sum_e alpha[e, h] * x[col(e), h, :]``.  Rows are the shard's own, so the
+    softmax needs no exchange; ``right`` (``[rows, heads]``) and ``x`` (``[rows, heads, width]``) go through the
+    needed-rows exchange, ``left`` is local.  The aggregation is the fused per-head weighted SpMM.
+    """
+
+    def __init__(self, rowptr, col, bounds: Sequence[int], heads: int, width: int, dtype, device, group=None,
+                 transport: str = "alltoall", negative_slope: float = 0.2):
+        from .bspmm import bspmm
+        from .ptr2ind import ptr2ind
+        from .scatter_softmax import scatter_softmax
+
+        self.heads, self.width, self.slope = heads, width, negative_slope
+        self.rows = rowptr.numel() - 1
+        self.edge_rows = ptr2ind(rowptr, col.numel())
+        self.softmax = scatter_softmax
+        self.logits = HaloShardedSddmm(rowptr, col, bounds, heads, dtype, device, group=group, transport=transport, op="add")
+        self.aggregate = HaloShardedSpmm(
+            rowptr, col, None, bounds, heads * width, dtype, device, group=group, transport=transport,
+            local_spmm=lambda ptr, c, alpha, x: bspmm(ptr, c, x.view(-1, heads, width), "mul", "sum", rhs=alpha))
+
+    def __call__(self, x_block: torch.Tensor, left_block: torch.Tensor, right_block: torch.Tensor) -> torch.Tensor:
+        scores = torch.nn.functional.leaky_relu(self.logits(left_block, right_block), self.slope)
+        self.aggregate.value = self.softmax(scores, self.edge_rows, 0, self.rows).unsqueeze(-1)
+        return self.aggregate(x_block.reshape(self.rows, self.heads * self.width))

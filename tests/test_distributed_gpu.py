@@ -69,6 +69,15 @@ def _worker(rank, world, port, result_dir):
         edge_op = HaloShardedSddmm(ptr, c, bounds, 64, left.dtype, device, transport=transport)
         results["dots_" + transport] = edge_op(left[bounds[rank]:bounds[rank + 1]].contiguous(),
                                                right[bounds[rank]:bounds[rank + 1]].contiguous()).cpu()
+    from ops_gnn.distributed import ShardedGatLayer
+
+    heads, width = 4, 64
+    feats = torch.randn(nodes, heads, width, generator=torch.Generator().manual_seed(45)).to(device)
+    el = torch.randn(nodes, heads, generator=torch.Generator().manual_seed(46)).to(device)
+    er = torch.randn(nodes, heads, generator=torch.Generator().manual_seed(47)).to(device)
+    own = slice(bounds[rank], bounds[rank + 1])
+    layer = ShardedGatLayer(ptr, c, bounds, heads, width, feats.dtype, device, transport="pull")
+    results["gat"] = layer(feats[own].contiguous(), el[own].contiguous(), er[own].contiguous()).cpu()
     torch.cuda.synchronize()
     torch.save(results, os.path.join(result_dir, f"rank{rank}.pt"))
     dist.barrier()
@@ -103,6 +112,16 @@ def test_sharded_spmm_two_gpus(tmp_path):
     for transport in ("alltoall", "pull"):
         got_dots = torch.cat([p["dots_" + transport] for p in parts])
         assert torch.equal(got_dots, want_dots), "sharded SDDMM, " + transport  # a dot product has one summation order
+    heads, width = 4, 64
+    feats = torch.randn(x.size(0), heads, width, generator=torch.Generator().manual_seed(45)).to("cuda:0")
+    el = torch.randn(x.size(0), heads, generator=torch.Generator().manual_seed(46)).to("cuda:0")
+    er = torch.randn(x.size(0), heads, generator=torch.Generator().manual_seed(47)).to("cuda:0")
+    edge_rows = ops_gnn.ptr2ind(rowptr, col.numel())
+    scores = torch.nn.functional.leaky_relu(ops_gnn.sddmm_csr(rowptr, col, el, er, "add", "u", "v"), 0.2)
+    alpha = ops_gnn.scatter_softmax(scores, edge_rows, 0, x.size(0))
+    want_gat = ops_gnn.bspmm(rowptr, col, feats, "mul", "sum", rhs=alpha.unsqueeze(-1)).cpu()
+    got_gat = torch.cat([p["gat"] for p in parts]).view(-1, heads, width)
+    assert float((got_gat - want_gat).abs().max()) <= 2e-5 * max(float(want_gat.abs().max()), 1.0), "sharded GAT layer"
     sent = sum(p["alltoall_exchange"][0] for p in parts)
     received = sum(p["alltoall_exchange"][1] for p in parts)
     assert sent == received and 0 < received < x.size(0)
