@@ -226,6 +226,8 @@ class HaloShardedSpmm:
         self._pulls.sort(key=lambda item: (item[0] - self.rank) % self.world)  # next rank first: no lockstep on one peer
         self._gather_into = _pybind.gather_rows
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        # pulls from different peers run side by side (each is a small launch with its own tail) on a few streams
+        self._pull_streams = [torch.cuda.Stream(device) for _ in range(min(4, max(len(self._pulls) - 1, 0)))]
 
     def _stream_barrier(self) -> None:
         self.dist.all_reduce(self._flag, group=self.group)  # ordered on the current stream; no host wait
@@ -240,8 +242,20 @@ class HaloShardedSpmm:
             self.own_block.copy_(x_block)
         if self.world > 1 and self.transport == "pull":
             self._stream_barrier()
-            for _, block, wanted, unit, start, count in self._pulls:
-                self._gather_into(block, wanted, unit, self.compact[start:start + count])
+            if not self._pull_streams:
+                for _, block, wanted, unit, start, count in self._pulls:
+                    self._gather_into(block, wanted, unit, self.compact[start:start + count])
+            else:
+                main = torch.cuda.current_stream()
+                ready = torch.cuda.Event()
+                ready.record(main)
+                for k, (_, block, wanted, unit, start, count) in enumerate(self._pulls):
+                    side = self._pull_streams[k % len(self._pull_streams)]
+                    side.wait_event(ready)
+                    with torch.cuda.stream(side):
+                        self._gather_into(block, wanted, unit, self.compact[start:start + count])
+                for side in self._pull_streams:
+                    main.wait_stream(side)
             self._stream_barrier()
         elif self.world > 1:
             packed = self.gather_rows(self.own_block, self.send_rows) if self.send_rows.numel() else \
