@@ -245,13 +245,16 @@ __device__ __forceinline__ int64_t ShuffleXor(int64_t v, int mask)
 
 // ---- bulk-copy (TMA 1-D) ring ------------------------------------------------------------------------------------
 #ifndef OPSGNN_BULK_STAGES
-#define OPSGNN_BULK_STAGES 3
+#define OPSGNN_BULK_STAGES 2
+#endif
+#ifndef OPSGNN_SUM_BLOCKS_PER_SM
+#define OPSGNN_SUM_BLOCKS_PER_SM 3  // resident blocks the lean bulk sum instances are compiled for (register budget)
 #endif
 #ifndef OPSGNN_BULK_STAGE_BYTES
-#define OPSGNN_BULK_STAGE_BYTES 4096
+#define OPSGNN_BULK_STAGE_BYTES 3072
 #endif
 constexpr int kBulkStages = OPSGNN_BULK_STAGES;            // stages per warp
-constexpr int kBulkStageBytes = OPSGNN_BULK_STAGE_BYTES;   // bytes per stage: 4 rows of 1 KiB, 8 of 512 B, ...
+constexpr int kBulkStageBytes = OPSGNN_BULK_STAGE_BYTES;   // bytes per stage: 3 rows of 1 KiB, 6 of 512 B, ...
 constexpr int kBulkWarpBytes = kBulkStages * kBulkStageBytes;
 constexpr int kBulkSmemBytes = kWarps * kBulkWarpBytes + kWarps * kBulkStages * 8;
 // Per-group weights (one per edge and feature group, e.g. attention heads) ride along with the rows of a stage: the
@@ -333,7 +336,8 @@ template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK> str
 // of two): p.lanes_per_row lanes share a gathered row and the 32 / lanes_per_row lane groups take different edges of
 // the same run, so no lane idles; the groups' partial results are merged with shuffles when the row ends.
 template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL, bool BULK, bool NARROW = false>
-__global__ void __launch_bounds__(kThreads, 2) ReduceKernel(const Params p)
+__global__ void __launch_bounds__(kThreads, (BULK && RK == kSum && !GENERAL && !NARROW) ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
+    ReduceKernel(const Params p)
 {
     static_assert(!NARROW || (BULK && NV == 1 && !GENERAL), "the narrow layout exists for lean bulk instances only");
     constexpr bool kRingAsync = NARROW;
