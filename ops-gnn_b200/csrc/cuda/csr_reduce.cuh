@@ -329,14 +329,14 @@ template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK> str
 // BULK = true gathers the dense rows with the bulk-copy engine instead of per-lane loads: one lane issues one
 // `cp.async.bulk` per gathered row segment (up to 1 KiB) into a per-warp ring of kBulkStages stages in shared
 // memory, completion is tracked by one mbarrier per stage, and the lanes read their 16-byte vectors back with
-// conflict-free shared loads.  Rows in flight then cost shared memory instead of registers: 12 KiB per warp instead
-// of 8, at 16 warps per SM, and the per-edge instruction count drops because one instruction moves a whole row.
+// conflict-free shared loads.  Rows in flight then cost shared memory instead of registers (6 KiB per warp), which
+// leaves room for three resident blocks per SM, and one instruction moves a whole row.
 //
 // NARROW = true (bulk only, NV == 1) is for rows narrower than one warp of 16-byte vectors (16 to 256 bytes, a power
 // of two): p.lanes_per_row lanes share a gathered row and the 32 / lanes_per_row lane groups take different edges of
 // the same run, so no lane idles; the groups' partial results are merged with shuffles when the row ends.
 template <class T, class O, class PtrT, class ColT, int VEC, int NV, int RK, bool GENERAL, bool BULK, bool NARROW = false>
-__global__ void __launch_bounds__(kThreads, (BULK && RK == kSum && !GENERAL && !NARROW) ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
+__global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
     ReduceKernel(const Params p)
 {
     static_assert(!NARROW || (BULK && NV == 1 && !GENERAL), "the narrow layout exists for lean bulk instances only");
