@@ -47,7 +47,7 @@ sys.path.insert(0, ROOT)
 RMAT = (0.57, 0.19, 0.19, 0.05)
 # dram__bytes_read.sum + dram__bytes_write.sum of one ReduceKernel launch, from a 1-pass ncu capture of this workload at
 # full size (a profiler figure, copied here; not measured by this script; the capture's summary is kept under profiles/)
-NCU_DRAM_TRAFFIC = {"rmat_s24_ef16_f256_fp32_spmm_sum": 203.65e9, "rmat_s24_ef16_f256_bf16_spmm_sum": 87.32e9}
+NCU_DRAM_TRAFFIC = {"rmat_s24_ef16_f256_fp32_spmm_sum": 203.84e9, "rmat_s24_ef16_f256_bf16_spmm_sum": 87.44e9}
 SEED = 20261125 + 4
 
 
