@@ -21,10 +21,11 @@ The line printed by rank 0 carries
 
 N > 1 (torchrun, one rank per GPU; strong scaling: the graph is fixed): output rows are split into contiguous ranges
 of equal work (edges + 6 per row).  X is owned by the same row ranges and each step moves only the rows of X a shard
-references into a compact buffer before the local SpMM: `--exchange pull` (default) runs the gather kernel once per
-peer with the peer's block (symmetric memory) as its source; `--exchange halo` packs the rows and sends them with one
-NCCL all-to-all (also the fallback when symmetric memory cannot be set up).  `--exchange allgather`: every rank owns
-an equal row block of X and each step all-gathers all of X.  The
+references into a compact buffer before the local SpMM: `--exchange pull` runs the gather kernel once per peer with
+the peer's block (symmetric memory) as its source; `--exchange halo` packs the rows and sends them with one NCCL
+all-to-all (also the fallback when symmetric memory cannot be set up).  The default `auto` takes pull between two
+GPUs and halo beyond.  `--exchange allgather`: every rank owns an equal row block of X and each step all-gathers all
+of X.  The
 `x_resident` record times the local SpMM alone.  The host-buffer leg at N > 1 uses the all-gather form, with shard
 bounds chosen for PCIe (a row weighs 50 edges there).
 `--impl reference` times the reference's CPU algorithm (the oracle port) on the host cores for the same metric.
@@ -171,9 +172,10 @@ def parse():
     parser.add_argument("--edge-factor", type=int, default=16)
     parser.add_argument("--feat", type=int, default=256)
     parser.add_argument("--dtype", default="fp32", choices=("fp32", "bf16"))
-    parser.add_argument("--exchange", default="pull", choices=("allgather", "halo", "pull"),
+    parser.add_argument("--exchange", default="auto", choices=("auto", "allgather", "halo", "pull"),
                         help="N > 1: all-gather of X; an all-to-all of only the rows each shard references (halo); or "
-                             "the same rows pulled from the peers' symmetric memory by the gather kernel (pull)")
+                             "the same rows pulled from the peers' symmetric memory by the gather kernel (pull); "
+                             "auto = pull between two GPUs (where it has been measured), halo beyond")
     parser.add_argument("--row-cost", type=float, default=6.0, help="N > 1: cost of one output row in edges (shard balance)")
     parser.add_argument("--e2e-row-cost", type=float, default=50.0, help="N > 1: the same for the host-buffer leg")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
@@ -245,6 +247,8 @@ def main():
             host_shard = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
                           for t in (*pieces, x[rank * block:(rank + 1) * block])]
             del pieces
+        if args.exchange == "auto":
+            args.exchange = "pull" if world == 2 else "halo"
         if args.exchange in ("halo", "pull"):
             # X is owned by the same row ranges as the output (a layer's output rows are the next layer's input)
             x_block = x[bounds[rank]:bounds[rank + 1]].clone()

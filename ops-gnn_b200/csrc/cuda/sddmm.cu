@@ -18,6 +18,9 @@ namespace opsgnn {
 namespace sddmm {
 
 constexpr int kThreads = 256;
+#ifndef OPSGNN_SDDMM_DOT_BLOCKS
+#define OPSGNN_SDDMM_DOT_BLOCKS 4  // resident blocks per SM the dot kernel is compiled for (63 registers at 4)
+#endif
 constexpr int kWarps = kThreads / 32;
 constexpr int kEdgesPerWarp = 64;
 constexpr int kEdgesPerCta = kWarps * kEdgesPerWarp;
@@ -213,7 +216,7 @@ __global__ void __launch_bounds__(kThreads) SddmmKernel(const Params p)
 // with lhs gathered by the CSR row (the caller swaps the operands when only rhs is) it is loaded once per row, not
 // once per edge.  Row ids are staged as 32-bit numbers; addresses are one 32 x 32 -> 64 multiply-add.
 template <class T, class IndexT, int VEC, int NVL>
-__global__ void __launch_bounds__(kThreads) SddmmDotKernel(const Params p)
+__global__ void __launch_bounds__(kThreads, OPSGNN_SDDMM_DOT_BLOCKS) SddmmDotKernel(const Params p)
 {
     __shared__ int s_a[kEdgesPerCta];
     __shared__ int s_b[kEdgesPerCta];
