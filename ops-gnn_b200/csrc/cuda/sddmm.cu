@@ -18,8 +18,8 @@ namespace opsgnn {
 namespace sddmm {
 
 constexpr int kThreads = 256;
-#ifndef OPSGNN_SDDMM_DOT_BLOCKS
-#define OPSGNN_SDDMM_DOT_BLOCKS 4  // resident blocks per SM the dot kernel is compiled for (63 registers at 4)
+#ifndef OPSGNN_SDDMM_DOT_MAX_VECTORS
+#define OPSGNN_SDDMM_DOT_MAX_VECTORS 4  // 16-byte vectors of each operand row a lane may own in the dot kernel
 #endif
 constexpr int kWarps = kThreads / 32;
 constexpr int kEdgesPerWarp = 64;
@@ -216,7 +216,7 @@ __global__ void __launch_bounds__(kThreads) SddmmKernel(const Params p)
 // with lhs gathered by the CSR row (the caller swaps the operands when only rhs is) it is loaded once per row, not
 // once per edge.  Row ids are staged as 32-bit numbers; addresses are one 32 x 32 -> 64 multiply-add.
 template <class T, class IndexT, int VEC, int NVL>
-__global__ void __launch_bounds__(kThreads, OPSGNN_SDDMM_DOT_BLOCKS) SddmmDotKernel(const Params p)
+__global__ void __launch_bounds__(kThreads, NVL == 4 ? 4 : 6) SddmmDotKernel(const Params p)
 {
     __shared__ int s_a[kEdgesPerCta];
     __shared__ int s_b[kEdgesPerCta];
@@ -345,7 +345,7 @@ template <class T> inline int DotVectorsPerLane(int64_t feat)
         return 0;
     }
     const int64_t vectors = feat / kVec;
-    for (int nvl = sizeof(T) == 4 ? 4 : 2; nvl >= 1; nvl >>= 1) {
+    for (int nvl = (sizeof(T) == 4 && OPSGNN_SDDMM_DOT_MAX_VECTORS >= 4) ? 4 : 2; nvl >= 1; nvl >>= 1) {
         if (vectors % nvl == 0) {
             const int64_t lanes = vectors / nvl;
             if (lanes <= 32 && (lanes & (lanes - 1)) == 0) {
