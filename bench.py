@@ -26,8 +26,8 @@ the peer's block (symmetric memory) as its source; `--exchange halo` packs the r
 all-to-all (also the fallback when symmetric memory cannot be set up).  The default `auto` takes pull between two
 GPUs and halo beyond.  `--exchange allgather`: every rank owns an equal row block of X and each step all-gathers all
 of X.  The
-`x_resident` record times the local SpMM alone.  The host-buffer leg at N > 1 uses the all-gather form, with shard
-bounds chosen for PCIe (a row weighs 50 edges there).
+`x_resident` record times the local SpMM alone.  The host-buffer leg at N > 1 uses the all-gather form with its own
+shard bounds (`--e2e-row-cost`).
 `--impl reference` times the reference's CPU algorithm (the oracle port) on the host cores for the same metric.
 """
 import argparse
@@ -177,7 +177,8 @@ def parse():
                              "the same rows pulled from the peers' symmetric memory by the gather kernel (pull); "
                              "auto = pull between two GPUs (where it has been measured), halo beyond")
     parser.add_argument("--row-cost", type=float, default=6.0, help="N > 1: cost of one output row in edges (shard balance)")
-    parser.add_argument("--e2e-row-cost", type=float, default=50.0, help="N > 1: the same for the host-buffer leg")
+    parser.add_argument("--e2e-row-cost", type=float, default=1.0,
+                        help="N > 1: the same for the host-buffer leg (measured at 4 GPUs: 272 ms per step with 1, 310 with 50)")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     return parser.parse_args()
@@ -239,8 +240,9 @@ def main():
         config["shard_rows"] = bounds[rank + 1] - bounds[rank]
         host_shard = None
         if not args.no_e2e:
-            # The host-buffer leg is bound by PCIe, where a row (1 KiB up as X, 1 KiB down as output) weighs as much
-            # as ~50 edges (20 bytes up each): it gets its own shard bounds and equal blocks of X.
+            # The host-buffer leg is bound by PCIe, not by the kernel: it gets its own shard bounds (balanced on edges +
+            # e2e_row_cost per row; weighing a row like the 50 edges its bytes amount to measured slower) and equal
+            # blocks of X.
             e2e_bounds = balanced_row_bounds(rowptr, world, row_cost=args.e2e_row_cost)
             block = nodes // world
             pieces = shard_csr(rowptr, col, value, e2e_bounds[rank], e2e_bounds[rank + 1])
