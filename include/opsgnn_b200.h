@@ -35,6 +35,7 @@ extern "C" {
 #define OPSGNN_ERR_UNSUPPORTED (-2) /* dtype or mode combination not built     */
 #define OPSGNN_ERR_WORKSPACE (-3)   /* workspace too small or misaligned       */
 #define OPSGNN_ERR_LIMIT (-4)       /* size beyond a documented fixed maximum  */
+#define OPSGNN_ERR_TIMEOUT (-5)     /* a bounded device-side wait ran out      */
 
 /* ---- dtype ids (0..4 as csrc/npu/torch_sparse_spmm/op_host/torch_sparse_spmm.cpp:19-36) */
 #define OPSGNN_F32 0
@@ -120,6 +121,29 @@ OPSGNN_API int opsgnn_csr_reduce_workspace_bytes(const OpsgnnCsrReduceDesc* desc
 OPSGNN_API int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* ptr, const void* col, const void* val,
                       const void* mat, void* out, int64_t* arg, const void* plan, void* workspace,
                       int64_t workspace_bytes, void* stream);
+
+/*
+ * Device-side waits and how a launch reports one that ran out.  The bulk-copy instances of the engine wait on an
+ * mbarrier for every stage of gathered rows.  Each wait is bounded (a poll limit, 2^15 polls of up to 100 us by
+ * default): a warp whose wait runs out counts itself in the 64-bit status word at the head of the launch's workspace
+ * (opsgnn_csr_reduce clears it before the launch), waits - bounded again - for its copies still in flight and returns
+ * without writing its remaining rows.  The launch itself always ends; its output is then incomplete.  This is the
+ * failure-detection contract the reference states for its device kernels (a device error surfaces as a status the
+ * host reads, never as a hang); the reference has no counterpart entry point because its runtime reports through
+ * aclrtSynchronizeStream.
+ *
+ * opsgnn_csr_reduce_status synchronises `stream`, copies the status word of `workspace` to the host and returns
+ * OPSGNN_OK when it is zero, OPSGNN_ERR_TIMEOUT otherwise (*stalled_waits = the count).
+ */
+OPSGNN_API int opsgnn_csr_reduce_status(const void* workspace, void* stream, int64_t* stalled_waits);
+/* Registers, for the current device, a second location (device-visible; mapped pinned host memory is the intended
+ * use) that a stalled wait also sets to 1, so a host that must not synchronise can poll it between launches.  NULL
+ * removes it.  The location must outlive every launch that was enqueued while it was registered. */
+OPSGNN_API int opsgnn_set_status_sink(void* sink);
+/* Poll limit of one wait for later launches (process-wide); negative restores the default.  Zero makes every
+ * bulk-copy wait give up at once without touching the barrier: the diagnostic that exercises the error path on a
+ * healthy GPU.  Copies in flight are still awaited with the default limit before a block exits. */
+OPSGNN_API int opsgnn_set_wait_polls(int64_t polls);
 
 /* Typed mean for integer sums (count wraps to the value dtype, truncating division, zero count gives 0):
  * out[b, r, k] /= narrow(ptr[r+1]-ptr[r]).  Follows MeanDivideRounded,

@@ -1,4 +1,5 @@
 // C ABI of the CSR reduce engine: plan construction, scratch sizing and dtype dispatch.
+#include <atomic>
 #include <cstdio>
 
 #include "csr_instances.h"
@@ -35,6 +36,14 @@ int KindOf(int reduce)
             return -1;
     }
 }
+
+// Head of every reduce workspace: the launch's status word (stalled waits), padded to the alignment of what follows.
+constexpr int64_t kStatusBytes = 256;
+
+// Per device: an optional second place where a stalled wait is reported, and the poll limit of one wait.
+constexpr int kMaxDevices = 64;
+std::atomic<unsigned long long*> g_status_sink[kMaxDevices];
+std::atomic<int64_t> g_wait_polls{-1};
 
 // Upper bound of a carry row: every feature tile is padded to at most 256 features.
 int64_t CarryWidth(const OpsgnnCsrReduceDesc& d) { return d.batches * AlignUp(d.feat > 0 ? d.feat : 1, 256); }
@@ -104,7 +113,8 @@ extern "C" int opsgnn_csr_reduce_workspace_bytes(const OpsgnnCsrReduceDesc* desc
     }
     const int64_t num_cta = NumCta(desc->rows, desc->nnz);
     const int64_t width = CarryWidth(*desc);
-    int64_t total = AlignUp(num_cta * 8, 256);                        // carry_row
+    int64_t total = kStatusBytes;                                      // status word
+    total += AlignUp(num_cta * 8, 256);                                // carry_row
     total += AlignUp(num_cta * width * AccBytes(desc->in_type), 256);  // carry_val
     if (KindOf(desc->reduce) == kExtremum) {
         total += AlignUp(num_cta * width * 8, 256);  // carry_arg
@@ -171,6 +181,13 @@ extern "C" int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* pt
     p.val_group = d.value_width > 0 ? d.feat / d.value_width : 1;
     char* cursor = static_cast<char*>(workspace);
     const int64_t width = CarryWidth(d);
+    p.status = reinterpret_cast<unsigned long long*>(cursor);
+    cursor += kStatusBytes;
+    int device = 0;
+    OPSGNN_CUDA_TRY(cudaGetDevice(&device));
+    p.status_sink = (device >= 0 && device < kMaxDevices) ? g_status_sink[device].load(std::memory_order_relaxed) : nullptr;
+    const int64_t polls = g_wait_polls.load(std::memory_order_relaxed);
+    p.wait_polls = polls < 0 ? kBulkSpinLimit : static_cast<uint32_t>(polls > 0xffffffffLL ? 0xffffffffLL : polls);
     p.carry_row = reinterpret_cast<int64_t*>(cursor);
     cursor += AlignUp(p.num_cta * 8, 256);
     p.carry_val = cursor;
@@ -179,6 +196,7 @@ extern "C" int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* pt
 
     const bool index64 = d.ptr_type == OPSGNN_I64;
     cudaStream_t s = AsStream(stream);
+    OPSGNN_CUDA_TRY(cudaMemsetAsync(p.status, 0, sizeof(unsigned long long), s));
 #ifdef OPSGNN_CHECKED
     // Diagnostic build only: run the launch synchronously and print the first out-of-range access it skipped.
     static unsigned long long* debug = nullptr;
@@ -319,6 +337,36 @@ extern "C" int opsgnn_csr_integer_mean(void* out, int out_type, const void* ptr,
     }
 }
 
+extern "C" int opsgnn_csr_reduce_status(const void* workspace, void* stream, int64_t* stalled_waits)
+{
+    if (workspace == nullptr || stalled_waits == nullptr) {
+        return OPSGNN_ERR_INVALID;
+    }
+    unsigned long long count = 0;
+    cudaStream_t s = AsStream(stream);
+    OPSGNN_CUDA_TRY(cudaMemcpyAsync(&count, workspace, sizeof(count), cudaMemcpyDeviceToHost, s));
+    OPSGNN_CUDA_TRY(cudaStreamSynchronize(s));
+    *stalled_waits = static_cast<int64_t>(count);
+    return count == 0 ? OPSGNN_OK : OPSGNN_ERR_TIMEOUT;
+}
+
+extern "C" int opsgnn_set_status_sink(void* sink)
+{
+    int device = 0;
+    OPSGNN_CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) {
+        return OPSGNN_ERR_LIMIT;
+    }
+    g_status_sink[device].store(static_cast<unsigned long long*>(sink), std::memory_order_relaxed);
+    return OPSGNN_OK;
+}
+
+extern "C" int opsgnn_set_wait_polls(int64_t polls)
+{
+    g_wait_polls.store(polls, std::memory_order_relaxed);
+    return OPSGNN_OK;
+}
+
 extern "C" const char* opsgnn_status_string(int status)
 {
     switch (status) {
@@ -332,6 +380,8 @@ extern "C" const char* opsgnn_status_string(int status)
             return "workspace too small or misaligned";
         case OPSGNN_ERR_LIMIT:
             return "size beyond a fixed maximum";
+        case OPSGNN_ERR_TIMEOUT:
+            return "a bounded device-side wait ran out of polls";
         default:
             return status > 0 ? cudaGetErrorString(static_cast<cudaError_t>(status)) : "unknown status";
     }

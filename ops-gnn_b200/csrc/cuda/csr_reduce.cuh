@@ -63,6 +63,9 @@ struct Params {
     int64_t num_cta;
     int64_t carry_stride;  // gridDim.y * TILE
     unsigned long long* debug;  // OPSGNN_CHECKED builds: {violations, first site, index, limit}
+    unsigned long long* status;       // head of the workspace: number of bulk waits that ran out of polls in this launch
+    unsigned long long* status_sink;  // optional second place for the same report (device-visible, e.g. mapped host memory)
+    uint32_t wait_polls;              // polls of one mbarrier wait before the warp gives up (kBulkSpinLimit by default)
     int tiles_per_batch;
     int mean;      // kSum: divide by the row's edge count
     int is_min;    // kExtremum
@@ -263,7 +266,9 @@ constexpr int kBulkWeightBytes = 128;  // per stage: rows per stage x weights pe
 constexpr int kBulkSmemBytesWeighted = kBulkSmemBytes + kWarps * kBulkStages * kBulkWeightBytes;
 // A failed try_wait may suspend the thread for up to this many nanoseconds (it wakes as soon as the phase completes),
 // so a waiting warp does not burn issue slots polling; the poll count bounds the wait to a few seconds in total, past
-// which the kernel flags an error and leaves.
+// which the warp counts itself in the launch's status word (Params::status, and Params::status_sink when one is
+// registered), waits - bounded again - for its copies still in flight and leaves its remaining rows unwritten.  The
+// host reads the status word and turns a non-zero count into an error; a launch never hangs on a copy.
 constexpr uint32_t kBulkWaitHintNs = 100000u;
 constexpr uint32_t kBulkSpinLimit = 1u << 15;
 
@@ -700,16 +705,23 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
             if (nb > 0) {
                 const uint32_t bar = bar_addr + (batch_id % kBulkStages) * 8;
                 const uint32_t parity = static_cast<uint32_t>(batch_id / kBulkStages) & 1u;
-                uint32_t spins = 0;
-                while (!MbarTryWait(bar, parity)) {
-                    if (++spins > kBulkSpinLimit) {  // never expected; leave an error mark instead of hanging
-                        stalled = true;
+                // At most p.wait_polls polls (each may sleep up to kBulkWaitHintNs); zero polls gives up at once, which
+                // is how the error path is exercised without a copy that never lands.
+                stalled = true;
+                for (uint32_t spins = 0; spins < p.wait_polls; ++spins) {
+                    if (MbarTryWait(bar, parity)) {
+                        stalled = false;
                         break;
                     }
                 }
-                if (stalled) {
-                    if (lane == 0 && p.debug != nullptr) {
-                        atomicAdd(p.debug, 1ULL);
+                stalled = __any_sync(0xffffffffu, stalled);  // one verdict per warp: lanes poll independently
+                if (stalled) {  // never expected: report it and leave instead of hanging
+                    if (lane == 0) {
+                        atomicAdd(p.status, 1ULL);
+                        if (p.status_sink != nullptr) {
+                            *reinterpret_cast<volatile unsigned long long*>(p.status_sink) = 1ULL;
+                            __threadfence_system();
+                        }
                     }
                     break;
                 }

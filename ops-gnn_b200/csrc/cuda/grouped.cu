@@ -50,7 +50,7 @@ __device__ __forceinline__ int64_t GroupOf(const Params& p, int64_t pos)
 
 __device__ __forceinline__ void AtomicMaxFloat(float* address, float v)
 {
-    if (v >= 0.0f) {
+    if (__float_as_int(v) >= 0) {  // the sign bit decides: -0.0 must take the unsigned path
         atomicMax(reinterpret_cast<int*>(address), __float_as_int(v));
     } else {
         atomicMin(reinterpret_cast<unsigned*>(address), __float_as_uint(v));

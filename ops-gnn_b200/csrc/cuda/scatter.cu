@@ -87,17 +87,20 @@ template <class S> __device__ __forceinline__ void AtomicMul(S* p, S v)
     }
 }
 
-// Extremum on floats through the integer view: non-negative floats order like signed ints, negative floats order in
-// reverse like unsigned ints.
+// Extremum on floats through the integer view: floats with a clear sign bit order like signed ints, floats with the sign
+// bit set order in reverse like unsigned ints.  The branch is on the sign BIT, not on `v >= 0`: -0.0 compares equal to
+// zero but its bits (0x80000000) are INT_MIN as a signed int, which would beat every stored negative in a signed min
+// and lose to everything in a signed max.  On the unsigned path -0.0 sits just below +0.0, where it belongs.
 __device__ __forceinline__ void AtomicExtremum(float* p, float v, bool is_min)
 {
+    const bool sign_clear = __float_as_int(v) >= 0;
     if (is_min) {
-        if (v >= 0.0f) {
+        if (sign_clear) {
             atomicMin(reinterpret_cast<int*>(p), __float_as_int(v));
         } else {
             atomicMax(reinterpret_cast<unsigned*>(p), __float_as_uint(v));
         }
-    } else if (v >= 0.0f) {
+    } else if (sign_clear) {
         atomicMax(reinterpret_cast<int*>(p), __float_as_int(v));
     } else {
         atomicMin(reinterpret_cast<unsigned*>(p), __float_as_uint(v));
@@ -105,13 +108,14 @@ __device__ __forceinline__ void AtomicExtremum(float* p, float v, bool is_min)
 }
 __device__ __forceinline__ void AtomicExtremum(double* p, double v, bool is_min)
 {
+    const bool sign_clear = __double_as_longlong(v) >= 0;
     if (is_min) {
-        if (v >= 0.0) {
+        if (sign_clear) {
             atomicMin(reinterpret_cast<long long*>(p), __double_as_longlong(v));
         } else {
             atomicMax(reinterpret_cast<unsigned long long*>(p), static_cast<unsigned long long>(__double_as_longlong(v)));
         }
-    } else if (v >= 0.0) {
+    } else if (sign_clear) {
         atomicMax(reinterpret_cast<long long*>(p), __double_as_longlong(v));
     } else {
         atomicMin(reinterpret_cast<unsigned long long*>(p), static_cast<unsigned long long>(__double_as_longlong(v)));

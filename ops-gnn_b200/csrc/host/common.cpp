@@ -1,6 +1,8 @@
 #include "common.h"
 
+#include <c10/cuda/CUDAException.h>
 #include <c10/util/intrusive_ptr.h>
+#include <cuda_runtime_api.h>
 
 #include <list>
 #include <mutex>
@@ -133,11 +135,65 @@ void ClearCsrFactsCache()
     g_facts.clear();
 }
 
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_sink_mutex;
+at::Tensor g_sink;               // int64[kMaxDevices] in pinned host memory: one stall word per device
+bool g_sink_registered[kMaxDevices] = {false};
+
+volatile int64_t* SinkWord(int device)
+{
+    if (device < 0 || device >= kMaxDevices) {
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_sink_mutex);
+    if (!g_sink.defined()) {
+        g_sink = at::zeros({kMaxDevices}, at::TensorOptions().dtype(at::kLong)).pin_memory();
+    }
+    int64_t* word = g_sink.data_ptr<int64_t>() + device;
+    if (!g_sink_registered[device]) {
+        // Pinned host memory is mapped into every device's address space at its host address (unified addressing).
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+        CheckStatus(opsgnn_set_status_sink(word), "status_sink");
+        g_sink_registered[device] = true;
+    }
+    return word;
+}
+
+}  // namespace
+
+int64_t DeviceStallCount(int device, bool synchronize)
+{
+    volatile int64_t* word = SinkWord(device);
+    if (word == nullptr) {
+        return 0;
+    }
+    if (synchronize) {
+        c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+        C10_CUDA_CHECK(cudaDeviceSynchronize());
+    }
+    const int64_t count = *word;
+    if (count != 0) {
+        *word = 0;
+    }
+    return count;
+}
+
+void RaiseIfDeviceStalled(const at::Tensor& on_device, const char* api)
+{
+    const int device = on_device.device().index();
+    TORCH_CHECK(DeviceStallCount(device, false) == 0, api,
+                ": device wait timed out in an earlier launch on cuda:", device,
+                " (a bulk-copy wait of the reduce kernel ran out of polls; that launch's output is incomplete)");
+}
+
 void RunCsrReduce(CsrReduceCall& call, const char* api)
 {
     if (call.rows == 0 || call.feat == 0 || call.batches == 0) {
         return;
     }
+    RaiseIfDeviceStalled(call.out, api);
     OpsgnnCsrReduceDesc desc{};
     desc.rows = call.rows;
     desc.src_rows = call.src_rows;

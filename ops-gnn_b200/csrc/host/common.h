@@ -95,6 +95,14 @@ struct CsrReduceCall {
 // Builds (or reuses) the plan, allocates carry scratch and launches the engine on the current stream.
 void RunCsrReduce(CsrReduceCall& call, const char* api);
 
+// Device-side waits that ran out (a bulk-copy wait of the reduce engine gave up; its launch left rows unwritten).  The
+// kernels report into one word of mapped pinned host memory per device, registered with the C ABI on the device's first
+// use, so the host can look without synchronising: every planner call looks first and raises for a stall of an EARLIER
+// launch (the asynchronous-error convention of CUDA itself).  DeviceStallCount(sync = true) synchronises the device
+// first, which makes the report cover everything enqueued so far.  Reading clears the word.
+void RaiseIfDeviceStalled(const at::Tensor& on_device, const char* api);
+int64_t DeviceStallCount(int device, bool synchronize);
+
 // Validation facts of a CSR structure: bit mask of opsgnn_csr_validate, cached like the plans.  Costs one 4-byte
 // device-to-host read on a miss.
 int CsrFacts(const at::Tensor& ptr, const std::optional<at::Tensor>& col, int64_t rows, int64_t cols, int64_t nnz);

@@ -38,6 +38,10 @@ void BindSpmm(py::module_& m)
     m.def("gather_rows", &GatherRows, py::arg("x"), py::arg("index"), py::arg("unit_ptr"), py::arg("out"),
           "out[i] = x[index[i]] through the CSR engine (unit_ptr = 0..n); not part of the reference binding",
           py::call_guard<py::gil_scoped_release>());
+    m.def("csr_spmm_into", &CsrSpmmInto, py::arg("ptr"), py::arg("col"), py::arg("value"), py::arg("x"), py::arg("out"),
+          "out[r] = sum_e value[e] * x[col[e]] into a caller-provided contiguous [rows, K] view; not part of the reference "
+          "binding",
+          py::call_guard<py::gil_scoped_release>());
     auto sub = m.def_submodule("torch_sparse_spmm", "torch_sparse SpMM on CUDA");
     sub.def("forward", &TorchSparseSpmmForward, py::arg("ptr"), py::arg("col"), py::arg("value"), py::arg("mat"),
             py::arg("reduce"), py::arg("outtype"), py::call_guard<py::gil_scoped_release>());
@@ -121,6 +125,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
         opsgnn::ClearCsrPlanCache();
         opsgnn::ClearCsrFactsCache();
     });
+    m.def(
+        "device_stall_count",
+        [](int64_t device, bool synchronize) { return opsgnn::DeviceStallCount(static_cast<int>(device), synchronize); },
+        py::arg("device"), py::arg("synchronize") = true,
+        "Device-side waits that ran out on this device since the last look (reading clears the count); with "
+        "synchronize the device is synchronised first so the count covers every launch enqueued so far",
+        py::call_guard<py::gil_scoped_release>());
+    m.def(
+        "set_wait_polls", [](int64_t polls) { opsgnn::CheckStatus(opsgnn_set_wait_polls(polls), "set_wait_polls"); },
+        py::arg("polls"),
+        "Poll limit of one device-side bulk-copy wait for later launches; negative restores the default, zero makes "
+        "every wait give up at once (the diagnostic that exercises the error path)");
     BindSegment(m);
     BindSpmm(m);
     BindConvert(m);

@@ -359,6 +359,57 @@ at::Tensor GatherRows(const at::Tensor& x, const at::Tensor& index, const at::Te
     return out;
 }
 
+// out[r, :] = sum_e value[e] * x[col[e], :] written into a caller-provided `out` (a row range of a larger matrix is
+// fine: any contiguous [rows, K] view).  The staged sharded SpMM produces its output stage by stage with this; the
+// structure is trusted (it was validated when the shard was built), so no validation pass runs here.
+at::Tensor CsrSpmmInto(const at::Tensor& ptr, const at::Tensor& col, const std::optional<at::Tensor>& value,
+                       const at::Tensor& x, const at::Tensor& out)
+{
+    const char* api = "csr_spmm_into";
+    for (const auto& tensor : {ptr, col, x, out}) {
+        TORCH_CHECK(tensor.defined() && tensor.device().is_cuda(), api, ": tensors must be CUDA tensors");
+        TORCH_CHECK(tensor.device() == out.device(), api, ": tensors must be on the same GPU");
+    }
+    TORCH_CHECK(x.dim() == 2 && out.dim() == 2 && x.is_contiguous() && out.is_contiguous(), api,
+                ": x and out must be contiguous matrices");
+    TORCH_CHECK(x.scalar_type() == out.scalar_type() && x.size(1) == out.size(1), api, ": x and out must agree in dtype and width");
+    TORCH_CHECK(x.scalar_type() == at::kFloat || x.scalar_type() == at::kHalf || x.scalar_type() == at::kBFloat16, api,
+                ": dtype must be float32, float16 or bfloat16");
+    TORCH_CHECK(ptr.dim() == 1 && col.dim() == 1 && ptr.numel() >= 1 && ptr.is_contiguous() && col.is_contiguous() &&
+                    (ptr.scalar_type() == at::kInt || ptr.scalar_type() == at::kLong) && col.scalar_type() == ptr.scalar_type(),
+                api, ": ptr and col must be contiguous int32/int64 vectors of one dtype");
+    const int64_t rows = ptr.numel() - 1;
+    TORCH_CHECK(out.size(0) == rows, api, ": out needs one row per CSR row");
+    TORCH_CHECK(!out.is_alias_of(x), api, ": out must not alias x");
+    if (value) {
+        TORCH_CHECK(value->defined() && value->device() == out.device() && value->scalar_type() == x.scalar_type() &&
+                        value->dim() == 1 && value->numel() == col.numel() && value->is_contiguous(),
+                    api, ": value must be a contiguous [E] vector of x's dtype");
+    }
+    if (rows == 0 || x.size(1) == 0) {
+        return out;
+    }
+    TORCH_CHECK(col.numel() == 0 || x.size(0) > 0, api, ": x has no rows");
+    c10::cuda::CUDAGuard guard(out.device());
+    CsrReduceCall call;
+    call.ptr = ptr;
+    call.col = col;
+    if (value) {
+        call.val = *value;
+        call.value_width = 1;
+    }
+    call.mat = x;
+    call.out = out;
+    call.rows = rows;
+    call.src_rows = x.size(0);
+    call.feat = x.size(1);
+    call.nnz = col.numel();
+    call.arg_none = col.numel();
+    call.reduce = OPSGNN_REDUCE_SUM;
+    RunCsrReduce(call, api);
+    return out;
+}
+
 at::Tensor SpmmSumCsr(const at::Tensor& indptr, const at::Tensor& indices, const at::Tensor& x,
                       const std::optional<at::Tensor>& out)
 {

@@ -51,7 +51,24 @@ from .scatter_log_softmax import scatter_log_softmax
 from .scatter_logsumexp import scatter_logsumexp
 from . import torch_sparse_spmm
 
+
+def check_device_status(device=None) -> None:
+    """Synchronise ``device`` and raise ``RuntimeError`` if a device-side wait of this library ran out since the last look.
+
+    Every wait inside the kernels is bounded; a wait that runs out makes its launch return with rows unwritten and
+    leaves a mark the host can read without a fault.  The operators look at the mark on every call (a stall of an
+    earlier launch raises there); this function is the explicit form for the end of a step.  No counterpart in the
+    reference, whose runtime reports device errors through its stream synchronisation.
+    """
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    count = _pybind.device_stall_count(int(index or 0), True)
+    if count:
+        raise RuntimeError(f"ops_gnn: device wait timed out on cuda:{index} (a bulk-copy wait of the reduce kernel ran "
+                           "out of polls; the output of that launch is incomplete)")
+
+
 __all__ = [
+    "check_device_status",
     "ind2ptr",
     "ptr2ind",
     "spmm",

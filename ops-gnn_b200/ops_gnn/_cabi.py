@@ -24,6 +24,7 @@ GROUPED_SOFTMAX, GROUPED_LOG_SOFTMAX, GROUPED_LOGSUMEXP = range(3)
 EXPORTS = (
     "opsgnn_status_string", "opsgnn_sm_count",
     "opsgnn_csr_plan_bytes", "opsgnn_csr_plan_build", "opsgnn_csr_reduce_workspace_bytes", "opsgnn_csr_reduce",
+    "opsgnn_csr_reduce_status", "opsgnn_set_status_sink", "opsgnn_set_wait_polls",
     "opsgnn_csr_integer_mean", "opsgnn_sddmm_workspace_bytes", "opsgnn_sddmm_csr", "opsgnn_sddmm_csr_static",
     "opsgnn_spmm_value_grad",
     "opsgnn_ind2ptr", "opsgnn_ptr2ind", "opsgnn_csr_validate", "opsgnn_permute_values", "opsgnn_index_stats",
@@ -71,6 +72,9 @@ _PROTOTYPES = {
     "opsgnn_csr_reduce_workspace_bytes": (c_int, [POINTER(CsrReduceDesc), POINTER(c_int64)]),
     "opsgnn_csr_reduce": (c_int, [POINTER(CsrReduceDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "opsgnn_csr_reduce_status": (c_int, [c_void_p, c_void_p, POINTER(c_int64)]),
+    "opsgnn_set_status_sink": (c_int, [c_void_p]),
+    "opsgnn_set_wait_polls": (c_int, [c_int64]),
     "opsgnn_csr_integer_mean": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),
     "opsgnn_sddmm_workspace_bytes": (c_int, [POINTER(SddmmDesc), POINTER(c_int64)]),
     "opsgnn_sddmm_csr": (c_int, [POINTER(SddmmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
@@ -142,10 +146,12 @@ def _stream(device):
 
 
 def csr_reduce(ptr, col, val, mat, reduce, *, rows=None, out_dtype=None, extremum=EXTREMUM_IGNORE_NAN,
-               arg_none=None, plan=None):
+               arg_none=None, plan=None, return_workspace=False):
     """Drive plan build + opsgnn_csr_reduce on CUDA tensors; returns (out, arg or None).
 
-    ``mat`` is ``[..., N, K]``; ``col`` may be None (segment reduction over consecutive rows).
+    ``mat`` is ``[..., N, K]``; ``col`` may be None (segment reduction over consecutive rows).  With
+    ``return_workspace`` the launch's workspace comes back as a third value (its head is the status word that
+    ``opsgnn_csr_reduce_status`` reads).
     """
     import torch
 
@@ -181,4 +187,16 @@ def csr_reduce(ptr, col, val, mat, reduce, *, rows=None, out_dtype=None, extremu
         arg = torch.empty(out.shape, dtype=torch.int64, device=device)
     check(lib.opsgnn_csr_reduce(ctypes.byref(desc), _ptr(ptr), _ptr(col), _ptr(val), _ptr(mat), _ptr(out), _ptr(arg),
                                 _ptr(plan), _ptr(workspace), workspace.numel(), stream), "csr_reduce")
+    if return_workspace:
+        return out, arg, workspace
     return out, arg
+
+
+def csr_reduce_status(workspace) -> int:
+    """Number of device-side waits that ran out in the launch that used ``workspace`` (synchronises its stream)."""
+    lib = load()
+    count = c_int64()
+    status = lib.opsgnn_csr_reduce_status(_ptr(workspace), _stream(workspace.device), ctypes.byref(count))
+    if status not in (0, -5):
+        check(status, "csr_reduce_status")
+    return count.value

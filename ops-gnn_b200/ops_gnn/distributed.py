@@ -5,7 +5,12 @@ its SpMM path.  Output rows are independent, so the graph is cut into contiguous
 edges (equal rows would leave the first shard of a power-law graph with most of the work).  Every rank owns one such
 range of the CSR structure and an equal block of the rows of the dense operand ``X``, as a GNN layer would hold them.
 One step is: all-gather the blocks of ``X`` into this GPU's own memory, then run the local SpMM over the rank's rows.
-The gathered matrix lands in local HBM before any kernel reads it; no kernel takes a peer pointer.
+
+Peer memory: no load anywhere in this module is a multicast load, and NVLS / multicast binding is switched off for
+the symmetric-memory buffers.  The NCCL forms land remote rows in the rank's own HBM before the SpMM reads them.  The
+``pull`` and ``push`` transports hand a peer's symmetric-memory block to this library's own gather kernel, as its
+source (``pull``: plain peer loads) or as its destination (``push``: plain peer stores); no library kernel of anybody
+else is ever given a peer pointer.
 
 ``feature_chunks > 1`` splits ``X`` by columns into contiguous chunk-major blocks: the all-gather of chunk ``c + 1``
 runs on a side stream while the SpMM of chunk ``c`` computes, so the transfer hides behind the math tile by tile.
@@ -128,7 +133,7 @@ class HaloShardedSpmm:
     set-up (once per graph) finds the distinct columns of the shard, tells every owner which of its rows are wanted,
     and relabels the shard's columns into a compact buffer ``[own rows | halo rows grouped by owner]``.  A step is
     then: pack the wanted rows per peer, one all-to-all with uneven splits that lands the halo in this GPU's memory,
-    and the local SpMM over the compact buffer.  No kernel reads peer memory.
+    and the local SpMM over the compact buffer (every kernel reads local memory only in this form).
 
     ``gather_rows(x, index)`` packs rows (default: the CSR engine run as a gather, a unit pointer array with the
     wanted rows as columns); ``local_spmm`` as in :class:`RowShardedSpmm`.
@@ -321,3 +326,236 @@ class ShardedGatLayer:
         scores = torch.nn.functional.leaky_relu(self.logits(left_block, right_block), self.slope)
         self.aggregate.value = self.softmax(scores, self.edge_rows, 0, self.rows).unsqueeze(-1)
         return self.aggregate(x_block.reshape(self.rows, self.heads * self.width))
+
+
+def staged_row_bounds(rowptr: torch.Tensor, fractions: Sequence[float], row_cost: float = 4.0) -> List[int]:
+    """Row boundaries that cut a shard into ``len(fractions)`` consecutive stages holding these shares of its work
+    (edges + ``row_cost`` per row)."""
+    rows = rowptr.numel() - 1
+    total = float(sum(fractions))
+    if rows < 0 or total <= 0 or any(f < 0 for f in fractions):
+        raise ValueError("stage fractions must be non-negative and not all zero")
+    work = rowptr.to(torch.float64) - float(rowptr[0]) + row_cost * torch.arange(rows + 1, dtype=torch.float64,
+                                                                              device=rowptr.device)
+    done, bounds = 0.0, [0]
+    for f in list(fractions)[:-1]:
+        done += f / total
+        target = torch.tensor([done * float(work[-1])], dtype=torch.float64, device=rowptr.device)
+        bounds.append(min(max(int(torch.searchsorted(work, target)), bounds[-1]), rows))
+    bounds.append(rows)
+    return bounds
+
+
+class StagedHaloSpmm:
+    """Needed-rows sharded SpMM whose exchange and product overlap stage by stage.
+
+    :class:`HaloShardedSpmm` finishes its whole exchange before the local SpMM starts.  Here the rank's rows are cut
+    into consecutive stages (``stage_fractions`` of the shard's work).  Stage ``k`` needs the rows of ``X`` its
+    columns reference that no earlier stage has already brought in; the compact buffer is laid out as
+    ``[own rows | new rows of stage 1 grouped by owner | new rows of stage 2 ... ]``.  The exchanges of all stages run
+    back to back on a side stream; the product of stage ``k`` waits only for exchange ``k`` and writes its own row
+    range of the output, so while stage ``k`` computes, stage ``k + 1`` is on the wire.  Every output row is still
+    produced by one kernel over all of its edges, in the order of the one-GPU product.
+
+    ``transport="alltoall"``: per stage, pack the wanted rows per peer (the CSR engine run as a gather) and one NCCL
+    all-to-all with uneven splits.  ``transport="push"`` (CUDA only): the compact buffers live in symmetric memory and
+    the gather kernel writes each wanted row straight into the requesting peer's buffer with plain peer stores - the
+    pack IS the transfer, no send buffer and no NCCL data path; stream-ordered one-element all-reduces mark "every
+    peer's stage-k rows have landed" and, at the start of a step, "nobody still reads last step's buffers".
+
+    ``spmm_into(ptr, col, value, x, out)`` and ``gather_rows(x, index, unit_ptr, out)`` default to the CUDA kernels; the
+    CPU tests pass stand-ins.
+    """
+
+    def __init__(self, rowptr, col, value, bounds: Sequence[int], feat: int, dtype, device, group=None,
+                 stage_fractions: Sequence[float] = (0.25, 0.25, 0.25, 0.25), row_cost: float = 4.0,
+                 transport: str = "alltoall", spmm_into: Optional[Callable] = None,
+                 gather_rows: Optional[Callable] = None):
+        import torch.distributed as dist
+
+        self.dist, self.group = dist, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if len(bounds) != self.world + 1:
+            raise ValueError("bounds must hold one row range per rank")
+        if transport not in ("alltoall", "push"):
+            raise ValueError("transport must be 'alltoall' or 'push'")
+        self.transport, self.feat, self.dtype, self.device = transport, feat, dtype, device
+        self.bounds = [int(b) for b in bounds]
+        self.own_first, own_last = self.bounds[self.rank], self.bounds[self.rank + 1]
+        self.own_rows = own_last - self.own_first
+        self.stage_rows = staged_row_bounds(rowptr, stage_fractions, row_cost)
+        stages = len(self.stage_rows) - 1
+        edges = torch.tensor(self.bounds, dtype=col.dtype, device=device)
+        cut = [int(v) for v in rowptr[torch.tensor(self.stage_rows, device=rowptr.device)].tolist()]
+
+        # per stage: the remote rows no earlier stage brings in, what every peer wants of this rank, and the splits
+        seen = col.new_empty(0)
+        fresh, self.want_splits, self.give_splits, self.send_rows = [], [], [], []
+        for k in range(stages):
+            needed = torch.unique(col[cut[k]:cut[k + 1]])
+            remote = needed[(needed < self.own_first) | (needed >= own_last)]
+            new = remote[~torch.isin(remote, seen)] if seen.numel() else remote      # sorted: grouped by owner
+            seen = torch.sort(torch.cat([seen, new])).values
+            owner = torch.searchsorted(edges, new, right=True) - 1
+            want = torch.bincount(owner, minlength=self.world)
+            give = torch.empty_like(want)
+            dist.all_to_all_single(give, want, group=group)
+            want_list, give_list = [int(c) for c in want.tolist()], [int(c) for c in give.tolist()]
+            wanted_of_me = torch.empty(sum(give_list), dtype=col.dtype, device=device)
+            dist.all_to_all_single(wanted_of_me, new.contiguous(), give_list, want_list, group=group)
+            rows_out = (wanted_of_me - self.own_first).contiguous()
+            if rows_out.numel() and (int(rows_out.min()) < 0 or int(rows_out.max()) >= self.own_rows):
+                raise RuntimeError("a peer asked for rows outside this rank's block: shard bounds disagree between ranks")
+            fresh.append(new)
+            self.want_splits.append(want_list)
+            self.give_splits.append(give_list)
+            self.send_rows.append(rows_out)
+        self.halo_counts = [int(n.numel()) for n in fresh]
+        self.halo_rows = sum(self.halo_counts)
+        self.halo_start = [self.own_rows]
+        for count in self.halo_counts:
+            self.halo_start.append(self.halo_start[-1] + count)
+
+        # compact column ids: own rows first, then the halo in the order it is received
+        arrival = torch.cat(fresh) if stages else col.new_empty(0)
+        ids, order = torch.sort(arrival)
+        is_own = (col >= self.own_first) & (col < own_last)
+        if ids.numel():
+            at = torch.searchsorted(ids, col).clamp_(max=ids.numel() - 1)
+            compact = torch.where(is_own, col - self.own_first, self.own_rows + order[at])
+        else:
+            compact = col - self.own_first
+        self.col = compact.contiguous()
+        self.stage_ptr = [(rowptr[self.stage_rows[k]:self.stage_rows[k + 1] + 1] - cut[k]).contiguous()
+                          for k in range(stages)]
+        self.stage_col = [self.col[cut[k]:cut[k + 1]] for k in range(stages)]
+        self.stage_val = [None if value is None else value[cut[k]:cut[k + 1]] for k in range(stages)]
+        self.unit_ptr = [torch.arange(rows.numel() + 1, dtype=col.dtype, device=device) for rows in self.send_rows]
+
+        total_rows = self.own_rows + self.halo_rows
+        if transport == "push":
+            self._setup_push(total_rows)
+        else:
+            self.compact = torch.empty((total_rows, feat), dtype=dtype, device=device)
+        self.own_block = self.compact[:self.own_rows]
+        if spmm_into is None or gather_rows is None:
+            from . import _pybind
+
+            spmm_into = spmm_into or _pybind.csr_spmm_into
+            gather_rows = gather_rows or _pybind.gather_rows
+        self.spmm_into, self.gather_rows = spmm_into, gather_rows
+        on_gpu = device.type == "cuda"
+        self.comm_stream = torch.cuda.Stream(device) if on_gpu else None
+        self.timing = False       # set it to collect CUDA events per phase of the next step (see phase_ms)
+        self._events = None
+
+    # ---- push transport: symmetric memory and where each peer wants this rank's rows ------------------------------
+    def _setup_push(self, total_rows: int) -> None:
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer stores only, no multicast binding
+        import torch.distributed._symmetric_memory as symm
+
+        dist, device = self.dist, self.device
+        most = torch.tensor([total_rows], dtype=torch.int64, device=device)
+        dist.all_reduce(most, op=dist.ReduceOp.MAX, group=self.group)
+        capacity = max(int(most.item()), 1)             # symmetric allocations have one size on every rank
+        buffer = symm.empty((capacity, self.feat), dtype=self.dtype, device=device)
+        self._handle = symm.rendezvous(buffer, self.group if self.group is not None else dist.group.WORLD)
+        self._buffer = buffer
+        self.compact = buffer[:total_rows]
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+        # For every stage, tell each owner where in this rank's compact buffer its rows go; learn the same from the peers.
+        self._push = []           # per stage: list of (peer block, first row in it, rows of my block to send, unit ptr)
+        for k, want in enumerate(self.want_splits):
+            starts, at = [], self.halo_start[k]
+            for count in want:
+                starts.append(at)
+                at += count
+            mine = torch.tensor(starts, dtype=torch.int64, device=device)
+            theirs = torch.empty_like(mine)
+            dist.all_to_all_single(theirs, mine, group=self.group)
+            theirs = [int(v) for v in theirs.tolist()]
+            plan, offset = [], 0
+            for peer, count in enumerate(self.give_splits[k]):
+                if peer != self.rank and count:
+                    block = self._handle.get_buffer(peer, (capacity, self.feat), self.dtype)
+                    rows = self.send_rows[k][offset:offset + count].contiguous()
+                    unit = torch.arange(count + 1, dtype=rows.dtype, device=device)
+                    plan.append((peer, block[theirs[peer]:theirs[peer] + count], rows, unit))
+                offset += count
+            plan.sort(key=lambda item: (item[0] - self.rank) % self.world)   # next rank first: no lockstep on one peer
+            self._push.append(plan)
+
+    def _stream_barrier(self) -> None:
+        self.dist.all_reduce(self._flag, group=self.group)  # ordered on the current stream; no host wait
+
+    def exchange_rows(self) -> Tuple[int, int]:
+        """(rows this rank sends, rows it receives) per step, over all stages."""
+        return sum(int(r.numel()) for r in self.send_rows), self.halo_rows
+
+    def _mark(self, name: str) -> None:
+        if self._events is not None:
+            event = torch.cuda.Event(enable_timing=True)
+            event.record(torch.cuda.current_stream())
+            self._events.append((name, event))
+
+    def _exchange_stage(self, k: int) -> None:
+        halo = self.compact[self.halo_start[k]:self.halo_start[k + 1]]
+        if self.transport == "push":
+            for _, target, rows, unit in self._push[k]:
+                self.gather_rows(self.own_block, rows, unit, target)
+            self._mark(f"pack{k}")
+            self._stream_barrier()                  # every peer's stage-k rows have landed here too
+        else:
+            if self.send_rows[k].numel():
+                packed = self.own_block.new_empty((self.send_rows[k].numel(), self.feat))
+                self.gather_rows(self.own_block, self.send_rows[k], self.unit_ptr[k], packed)
+            else:
+                packed = self.own_block.new_empty((0, self.feat))
+            self._mark(f"pack{k}")
+            self.dist.all_to_all_single(halo, packed, self.want_splits[k], self.give_splits[k], group=self.group)
+        self._mark(f"exchange{k}")
+
+    def __call__(self, x_block: torch.Tensor) -> torch.Tensor:
+        if x_block.data_ptr() != self.own_block.data_ptr():
+            self.own_block.copy_(x_block)
+        stages = len(self.stage_ptr)
+        out = self.own_block.new_empty((self.own_rows, self.feat))
+        self._events = [] if (self.timing and self.comm_stream is not None) else None
+        if self.comm_stream is None:                # CPU ranks (tests): the same order without streams
+            for k in range(stages):
+                if self.world > 1:
+                    self._exchange_stage(k)
+            for k in range(stages):
+                first, last = self.stage_rows[k], self.stage_rows[k + 1]
+                self.spmm_into(self.stage_ptr[k], self.stage_col[k], self.stage_val[k], self.compact, out[first:last])
+            return out
+        main, comm = torch.cuda.current_stream(), self.comm_stream
+        comm.wait_stream(main)                      # the block is in place; last step's products are enqueued before
+        landed = []
+        with torch.cuda.stream(comm):
+            self._mark("start")
+            if self.world > 1 and self.transport == "push":
+                self._stream_barrier()              # nobody still reads the halo this step overwrites
+            for k in range(stages):
+                if self.world > 1:
+                    self._exchange_stage(k)
+                event = torch.cuda.Event()
+                event.record(comm)
+                landed.append(event)
+        for k in range(stages):
+            main.wait_event(landed[k])
+            first, last = self.stage_rows[k], self.stage_rows[k + 1]
+            self.spmm_into(self.stage_ptr[k], self.stage_col[k], self.stage_val[k], self.compact, out[first:last])
+            self._mark(f"product{k}")
+        comm.wait_stream(main)                      # scratch allocated on either stream is not reused across the join
+        return out
+
+    def phase_ms(self):
+        """After a step run with ``timing = True`` (and a device synchronise): milliseconds from the step's start to the
+        end of every phase, in the order the phases were enqueued."""
+        if not self._events:
+            return {}
+        start = self._events[0][1]
+        return {name: start.elapsed_time(event) for name, event in self._events[1:]}

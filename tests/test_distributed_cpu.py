@@ -92,6 +92,63 @@ def _halo_worker(rank, world, port, result_dir):
     dist.destroy_process_group()
 
 
+def _staged_worker(rank, world, port, fractions, result_dir):
+    import sys
+
+    for path in (ROOT, PACKAGE_DIR):
+        if path not in sys.path:
+            sys.path.insert(0, path)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from ops_gnn.distributed import StagedHaloSpmm, balanced_row_bounds, shard_csr, staged_row_bounds
+    from oracle.spmm import csr_spmm_sum_vectorised
+
+    rowptr, col, value, _ = _make_graph()
+    x = torch.randn(rowptr.numel() - 1, 12, generator=torch.Generator().manual_seed(5))
+    col = col * 6 % x.size(0)
+    bounds = balanced_row_bounds(rowptr, world, row_cost=1.0)
+    ptr, c, v = shard_csr(rowptr, col, value, bounds[rank], bounds[rank + 1])
+    op = StagedHaloSpmm(ptr, c, v, bounds, x.size(1), x.dtype, torch.device("cpu"), stage_fractions=fractions,
+                        row_cost=1.0,
+                        spmm_into=lambda p_, c_, v_, mat, out: out.copy_(csr_spmm_sum_vectorised(p_, c_, v_, mat)),
+                        gather_rows=lambda block, index, unit, out: out.copy_(block[index]))
+    out = op(x[bounds[rank]:bounds[rank + 1]])
+    assert torch.equal(out, op(op.own_block))                    # producing the block in place skips the copy
+    stage_bounds = staged_row_bounds(ptr, fractions, row_cost=1.0)
+    assert stage_bounds == op.stage_rows and stage_bounds[0] == 0 and stage_bounds[-1] == ptr.numel() - 1
+    assert all(a <= b for a, b in zip(stage_bounds, stage_bounds[1:]))
+    # every remote row is fetched once, by the first stage that references it
+    remote = torch.unique(c[(c < bounds[rank]) | (c >= bounds[rank + 1])])
+    assert op.exchange_rows()[1] == remote.numel() == sum(op.halo_counts)
+    torch.save({"out": out, "exchange": op.exchange_rows(), "col": col, "stages": op.halo_counts},
+               os.path.join(result_dir, f"staged{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _check_staged(world, fractions, tmp_path):
+    mp.spawn(_staged_worker, args=(world, _free_port(), fractions, str(tmp_path)), nprocs=world, join=True)
+    parts = [torch.load(tmp_path / f"staged{r}.pt") for r in range(world)]
+    rowptr, _, value, _ = _make_graph()
+    x = torch.randn(rowptr.numel() - 1, 12, generator=torch.Generator().manual_seed(5))
+    from oracle.spmm import csr_spmm_sum_vectorised
+
+    want = csr_spmm_sum_vectorised(rowptr, parts[0]["col"], value, x)
+    got = torch.cat([p["out"] for p in parts], dim=0)
+    assert torch.allclose(got, want, rtol=1e-5, atol=1e-5)
+    assert sum(p["exchange"][0] for p in parts) == sum(p["exchange"][1] for p in parts) > 0
+    return parts
+
+
+def test_staged_halo_spmm_gloo(tmp_path):
+    """Exchange and product overlap stage by stage: three stages on two ranks, an empty stage, and three ranks."""
+    parts = _check_staged(2, (0.2, 0.3, 0.5), tmp_path)
+    assert all(len(p["stages"]) == 3 for p in parts)
+    _check_staged(2, (0.5, 0.0, 0.5), tmp_path)
+    _check_staged(3, (1.0,), tmp_path)
+
+
 def test_halo_sharded_spmm_gloo(tmp_path):
     world = 2
     mp.spawn(_halo_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
