@@ -9,25 +9,32 @@ default (scale 24, feat 256, fp32: 16.7M nodes, 256M drawn edges) is the configu
 All inputs are seeded synthetic tensors generated on the GPU; no dataset is read.
 
 The line printed by rank 0 carries
-  value       whole-job nnz*feat/s with inputs resident in HBM (CUDA events, K steps, max over ranks),
-  e2e         the same metric through the public API `ops_gnn.torch_sparse_spmm.csr_spmm` with HOST buffers: the
-              pinned-host -> device copies of rowptr/col/value/X and the device -> host copy of the result are inside
-              the timed region (N > 1: every rank moves its own CSR slice, block of X and output rows through
-              `ops_gnn.distributed.RowShardedSpmm`),
-  roofline    algorithmic bytes of one step / measured step time against the measured HBM copy bandwidth,
+  value         whole-job nnz*feat/s with inputs resident in HBM (CUDA events, K steps, max over ranks),
+  e2e           the same metric through the public API `ops_gnn.torch_sparse_spmm.csr_spmm` with HOST buffers: the
+                pinned-host -> device copies of rowptr/col/value/X and the device -> host copy of the result are inside
+                the timed region (N > 1: every rank moves its own CSR slice, block of X and output rows through
+                `ops_gnn.distributed.RowShardedSpmm`),
+  roofline      algorithmic bytes of one step / measured step time against the measured HBM copy bandwidth (N > 1: per
+                rank, the local product alone),
+  parity_check  rows of the timed product copied to the host and compared with the float64 CPU oracle of the same rows
+                (N > 1: every rank checks rows of its own shard against the oracle fed with the TRUE rows of X, so a
+                wrong exchange shows; the verdicts are reduced over the ranks),
   cpu_baseline  the CPU oracle (vectorised restatement of the reference's golden) on a bounded row sample, all host
-              threads,
-  clocks      SM clock and throttle reasons sampled by nvidia-smi during the timed region.
+                threads (N = 1 only),
+  ops           N = 1 only: the other half of the metric - `sddmm_csr` dot on BASELINE config 3 (nnz/s, roofline) - and
+                the GAT layer of config 5, measured by the functions of bench_ops.py after the timed SpMM,
+  clocks        SM clock and throttle reasons sampled by nvidia-smi during the timed region.
 
 N > 1 (torchrun, one rank per GPU; strong scaling: the graph is fixed): output rows are split into contiguous ranges
-of equal work (edges + 6 per row).  X is owned by the same row ranges and each step moves only the rows of X a shard
-references into a compact buffer before the local SpMM: `--exchange pull` runs the gather kernel once per peer with
-the peer's block (symmetric memory) as its source; `--exchange halo` packs the rows and sends them with one NCCL
-all-to-all (also the fallback when symmetric memory cannot be set up).  The default `auto` takes pull between two
-GPUs and halo beyond.  `--exchange allgather`: every rank owns an equal row block of X and each step all-gathers all
-of X.  The
-`x_resident` record times the local SpMM alone.  The host-buffer leg at N > 1 uses the all-gather form with its own
-shard bounds (`--e2e-row-cost`).
+of equal work (edges + 6 per row) and X is owned by the same row ranges.  Each step moves only the rows of X a shard
+references.  `--exchange staged` (the default) cuts every shard into consecutive row stages whose exchanges (pack +
+NCCL all-to-all) run back to back on a side stream while the products of earlier stages compute;
+`--exchange staged_push` is the same pipeline with the gather kernel storing the rows straight into the peers'
+symmetric-memory buffers instead of pack + NCCL; `--exchange halo` / `pull` are the unstaged forms (whole exchange,
+then the product); `--exchange allgather` all-gathers all of X.  `sharding.phases_ms` gives, for one extra step after
+the timed region, the time from the step's start to the end of every phase (max over ranks); the `x_resident` record
+times the local SpMM alone.  The host-buffer leg at N > 1 uses the all-gather form with its own shard bounds
+(`--e2e-row-cost`).
 `--impl reference` times the reference's CPU algorithm (the oracle port) on the host cores for the same metric.
 """
 import argparse
@@ -135,28 +142,47 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(clocks)}
 
 
-# ---- CPU arm ----------------------------------------------------------------------------------------------------------------
-def cpu_sample(rowptr, col, value, x, target_edges):
-    """Contiguous row range around the median edge holding about `target_edges` edges (host tensors)."""
-    nnz = int(rowptr[-1])
-    middle = nnz // 2
-    first = int(torch.searchsorted(rowptr, torch.tensor(middle), right=True)) - 1
-    last = int(torch.searchsorted(rowptr, torch.tensor(min(middle + target_edges, nnz)), right=False))
-    last = max(last, first + 1)
-    lo, hi = int(rowptr[first]), int(rowptr[last])
-    return (rowptr[first:last + 1] - lo).clone(), col[lo:hi].clone(), value[lo:hi].clone(), first, last
+# ---- CPU arm and parity sample ---------------------------------------------------------------------------------------------
+def row_sample(rowptr, col, value, x_rows_of, target_edges, base=0):
+    """A contiguous row range around the median edge of (rowptr, col) holding about `target_edges` edges, as a graph of
+    its own on the host: pointers rebased, columns relabelled to the distinct rows they reference, and those rows of X
+    (`x_rows_of(ids)` gathers them on the device).  Returns a dict of host tensors plus the row range."""
+    nnz = int(rowptr[-1]) - int(rowptr[0])
+    start = int(rowptr[0])
+    probe = torch.tensor([start + nnz // 2, start + min(nnz // 2 + target_edges, nnz)], device=rowptr.device, dtype=rowptr.dtype)
+    first = max(int(torch.searchsorted(rowptr, probe[:1], right=True)) - 1, 0)
+    last = min(max(int(torch.searchsorted(rowptr, probe[1:], right=False)), first + 1), rowptr.numel() - 1)
+    lo, hi = int(rowptr[first]) - start, int(rowptr[last]) - start
+    distinct, local = torch.unique(col[lo:hi], return_inverse=True)
+    return {"ptr": (rowptr[first:last + 1] - rowptr[first]).cpu(), "col": local.cpu(), "value": value[lo:hi].float().cpu(),
+            "x": x_rows_of(distinct).float().cpu(), "first": first + base, "last": last + base, "rows": (first, last),
+            "edges": hi - lo}
 
 
-def time_cpu(rowptr, col, value, x, repeats):
+def parity_of(sample, gpu_rows, tolerance):
+    """Largest |gpu - oracle| over the sample's rows, relative to the magnitude each row summed (float64 oracle)."""
+    from oracle.spmm import csr_spmm_sum_vectorised
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    want = csr_spmm_sum_vectorised(sample["ptr"], sample["col"], sample["value"].double(), sample["x"].double())
+    size = csr_spmm_sum_vectorised(sample["ptr"], sample["col"], sample["value"].double().abs(), sample["x"].double().abs())
+    error = float(((gpu_rows.double().cpu() - want).abs() / size.clamp(min=1.0)).max()) if want.numel() else 0.0
+    return {"rows": [sample["first"], sample["last"]], "edges": sample["edges"], "max_rel_err": error,
+            "tolerance": tolerance, "ok": bool(error <= tolerance),
+            "oracle": "oracle.spmm.csr_spmm_sum_vectorised in float64; error relative to max(1, sum |w x|) of the row"}
+
+
+def time_cpu(sample, repeats):
     from oracle.spmm import csr_spmm_sum_vectorised
 
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    csr_spmm_sum_vectorised(rowptr, col, value, x)  # warm the allocator and the thread pool
+    args = (sample["ptr"], sample["col"], sample["value"], sample["x"])
+    csr_spmm_sum_vectorised(*args)  # warm the allocator and the thread pool
     times = []
     for _ in range(repeats):
         start = time.perf_counter()
-        csr_spmm_sum_vectorised(rowptr, col, value, x)
+        csr_spmm_sum_vectorised(*args)
         times.append(time.perf_counter() - start)
     return min(times), threads
 
@@ -172,20 +198,29 @@ def parse():
     parser.add_argument("--edge-factor", type=int, default=16)
     parser.add_argument("--feat", type=int, default=256)
     parser.add_argument("--dtype", default="fp32", choices=("fp32", "bf16"))
-    parser.add_argument("--exchange", default="auto", choices=("auto", "allgather", "halo", "pull"),
-                        help="N > 1: all-gather of X; an all-to-all of only the rows each shard references (halo); or "
-                             "the same rows pulled from the peers' symmetric memory by the gather kernel (pull); "
-                             "auto = pull between two GPUs (where it has been measured), halo beyond")
+    parser.add_argument("--exchange", default="auto",
+                        choices=("auto", "staged", "staged_push", "allgather", "halo", "pull"),
+                        help="N > 1: staged = row stages whose pack + NCCL all-to-all overlap with the products of "
+                             "earlier stages; staged_push = the same with the gather kernel storing into the peers' "
+                             "symmetric memory; halo / pull = the unstaged forms; allgather = all of X every step; "
+                             "auto = staged")
+    parser.add_argument("--stages", default="0.2,0.25,0.3,0.25",
+                        help="staged exchanges: shares of a shard's work per stage, in row order")
     parser.add_argument("--row-cost", type=float, default=6.0, help="N > 1: cost of one output row in edges (shard balance)")
     parser.add_argument("--e2e-row-cost", type=float, default=1.0,
                         help="N > 1: the same for the host-buffer leg (measured at 4 GPUs: 272 ms per step with 1, 310 with 50)")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    parser.add_argument("--no-ops", action="store_true", help="skip the SDDMM / GAT legs (profiling runs)")
     return parser.parse_args()
 
 
 def workload_name(args):
     return f"rmat_s{args.scale}_ef{args.edge_factor}_f{args.feat}_{args.dtype}_spmm_sum"
+
+
+SAMPLE_EDGES = 1 << 22          # CPU sample of the N = 1 run (timed as the CPU baseline and used as the parity check)
+SHARD_SAMPLE_EDGES = 1 << 20    # parity sample of every rank at N > 1
 
 
 def main():
@@ -203,12 +238,17 @@ def main():
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     distributed = world > 1 and args.impl == "ours"
+    args.host_binding = bind_near_gpu(local) if distributed else None
     if distributed:
+        # plain peer loads / stores and NCCL rings only: no NVLS, no multicast binding of symmetric memory
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=device)
     dtype = torch.float32 if args.dtype == "fp32" else torch.bfloat16
     elem = 4 if dtype == torch.float32 else 2
+    tolerance = 1e-5 if dtype == torch.float32 else 1e-2
     nodes = 1 << args.scale
 
     # ---- inputs (seeded; identical on every rank) ------------------------------------------------------------------
@@ -217,6 +257,7 @@ def main():
     gen = torch.Generator(device=device).manual_seed(SEED + 1)
     value = torch.rand(nnz, device=device, generator=gen).to(dtype)
     x = torch.randn(nodes, args.feat, device=device, generator=gen, dtype=torch.float32).to(dtype)
+    # the same keys in both arms: the driver compares the two `config` objects
     config = {"workload": workload_name(args), "nodes": nodes, "nnz": nnz, "feat": args.feat,
               "index_dtype": "int64", "l2": "inputs_larger_than_l2", "seed": SEED}
 
@@ -228,16 +269,20 @@ def main():
 
     forward = ops_gnn._pybind.torch_sparse_spmm.forward
     out_code = 0 if dtype == torch.float32 else 2
+    sharding = {"parallelism": "single_gpu"}
 
-    # ---- shard (nnz-balanced contiguous row ranges) ---------------------------------------------------------------------
+    # ---- shard (work-balanced contiguous row ranges) -------------------------------------------------------------------
     sharded = None
     if distributed:
-        from ops_gnn.distributed import HaloShardedSpmm, RowShardedSpmm, balanced_row_bounds, shard_csr
+        from ops_gnn.distributed import (HaloShardedSpmm, RowShardedSpmm, StagedHaloSpmm, balanced_row_bounds, shard_csr)
 
         # a row end costs the kernel about four edges on this graph (measured per rank: 0.13 ns per edge, 0.6 ns per row)
         bounds = balanced_row_bounds(rowptr, world, row_cost=args.row_cost)
         my_ptr, my_col, my_val = shard_csr(rowptr, col, value, bounds[rank], bounds[rank + 1])
-        config["shard_rows"] = bounds[rank + 1] - bounds[rank]
+        sharding = {"shard_rows": [bounds[k + 1] - bounds[k] for k in range(world)], "row_cost": args.row_cost}
+        # parity sample of this rank, taken while all of X is still here: rows of the shard around its median edge with
+        # the TRUE rows of X they reference (global column ids), so the check below does not depend on the exchange
+        sample = row_sample(my_ptr, my_col, my_val, lambda ids: x[ids], SHARD_SAMPLE_EDGES, base=bounds[rank])
         host_shard = None
         if not args.no_e2e:
             # The host-buffer leg is bound by PCIe, not by the kernel: it gets its own shard bounds (balanced on edges +
@@ -250,46 +295,57 @@ def main():
                           for t in (*pieces, x[rank * block:(rank + 1) * block])]
             del pieces
         if args.exchange == "auto":
-            args.exchange = "pull" if world == 2 else "halo"
-        if args.exchange in ("halo", "pull"):
+            args.exchange = "staged"
+        if args.exchange in ("halo", "pull", "staged", "staged_push"):
             # X is owned by the same row ranges as the output (a layer's output rows are the next layer's input)
             x_block = x[bounds[rank]:bounds[rank + 1]].clone()
             del rowptr, col, value, x
             torch.cuda.empty_cache()
-            transport = "pull" if args.exchange == "pull" else "alltoall"
+            fractions = [float(f) for f in args.stages.split(",")]
+
+            def build(kind):
+                if kind in ("staged", "staged_push"):
+                    return StagedHaloSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device,
+                                          stage_fractions=fractions, row_cost=args.row_cost,
+                                          transport="push" if kind == "staged_push" else "alltoall")
+                return HaloShardedSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device,
+                                       transport="pull" if kind == "pull" else "alltoall")
+
+            fallback = {"staged_push": "staged", "pull": "halo"}
             try:
-                sharded = HaloShardedSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device, transport=transport)
-                failure = None
+                sharded, failure = build(args.exchange), None
             except (RuntimeError, ImportError, AttributeError) as exc:  # symmetric memory unavailable on this box
                 sharded, failure = None, f"{type(exc).__name__}: {exc}"[:200]
             agreed = torch.tensor([0 if failure else 1], device=device)
             dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
             if int(agreed.item()) == 0:  # every rank falls back together
-                if transport == "alltoall":
+                if args.exchange not in fallback:
                     raise RuntimeError(f"sharded SpMM set-up failed: {failure}")
                 sharded = None
                 torch.cuda.empty_cache()
-                sharded = HaloShardedSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device, transport="alltoall")
-                args.exchange = "halo"
-                config["exchange_fallback"] = failure or "symmetric memory set-up failed on another rank"
-            my_col = sharded.col
-            x = sharded.compact
+                args.exchange = fallback[args.exchange]
+                sharded = build(args.exchange)
+                sharding["exchange_fallback"] = failure or "symmetric memory set-up failed on another rank"
+            x_block = sharded.own_block.copy_(x_block)        # produce the block where the exchange reads it
             sent, received = sharded.exchange_rows()
-            config["parallelism"] = (f"row_shard{world}_halo_pull_x" if args.exchange == "pull"
-                                     else f"row_shard{world}_halo_alltoall_x")
-            config["halo_rows_rank0"] = {"sent": sent, "received": received}
+            sharding["parallelism"] = f"row_shard{world}_{args.exchange}_x"
+            sharding["halo_rows_rank0"] = {"sent": sent, "received": received}
+            if args.exchange.startswith("staged"):
+                sharding["stage_fractions"] = fractions
+                sharding["stage_halo_rows_rank0"] = sharded.halo_counts
+            local_ptr, local_col, local_x = my_ptr, sharded.col, sharded.compact
         else:
             block = nodes // world
             x_block = x[rank * block:(rank + 1) * block].clone()
             del rowptr, col, value, x
             torch.cuda.empty_cache()
             sharded = RowShardedSpmm(my_ptr, my_col, my_val, block, args.feat, dtype, device)
-            x = sharded.gathered[0]  # filled by the all-gather of every step, never by the generator
-            config["parallelism"] = f"row_shard{world}_allgather_x"
+            local_ptr, local_col, local_x = my_ptr, my_col, sharded.gathered[0]  # filled by every step's all-gather
+            sharding["parallelism"] = f"row_shard{world}_allgather_x"
     else:
         my_ptr, my_col, my_val = rowptr, col, value
         x_block = None
-        config["parallelism"] = "single_gpu"
+        sample = None if args.no_cpu else row_sample(rowptr, col, value, lambda ids: x[ids], SAMPLE_EDGES)
 
     def step():
         if distributed:
@@ -320,14 +376,30 @@ def main():
     if distributed:
         dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
     ms_per_step = float(elapsed.item()) / args.steps
+    ops_gnn.check_device_status()      # a device-side wait that ran out would have left rows unwritten: fail loudly
 
-    # kernel-only scaling figure for N > 1: the same local SpMM with X already replicated
+    # ---- parity: rows of the timed product against the float64 CPU oracle -------------------------------------------------
+    parity = None
+    if sample is not None:
+        first, last = sample["rows"]
+        parity = parity_of(sample, out[first:last], tolerance)
+        if distributed:
+            verdict = torch.tensor([1.0 if parity["ok"] else 0.0, -parity["max_rel_err"]], device=device, dtype=torch.float64)
+            dist.all_reduce(verdict, op=dist.ReduceOp.MIN)
+            edges = torch.tensor([parity["edges"]], device=device)
+            dist.all_reduce(edges)
+            parity = {"ok": bool(verdict[0].item() == 1.0), "max_rel_err": -float(verdict[1].item()), "tolerance": tolerance,
+                      "ranks_checked": world, "edges": int(edges.item()), "rows_rank0": parity["rows"],
+                      "oracle": parity["oracle"] + "; every rank checks rows of its own shard against the oracle fed "
+                                "with the true rows of X (taken before X was sharded)"}
+
+    # ---- N > 1: the local product alone, per-phase times of one more step, per-rank roofline ---------------------------
     resident_ms = None
     if distributed:
         barrier()
         start.record()
         for _ in range(args.steps):
-            forward(my_ptr, my_col, my_val, x, 0, out_code)
+            forward(local_ptr, local_col, my_val, local_x, 0, out_code)
         stop.record()
         barrier()
         local_ms = torch.tensor([start.elapsed_time(stop) / args.steps], device=device)
@@ -335,69 +407,188 @@ def main():
         dist.all_gather_into_tensor(every_ms, local_ms)
         resident_ms = float(every_ms.max().item())
         resident_per_rank = [round(v, 3) for v in every_ms.tolist()]
+        shard_bytes = torch.tensor([float(algorithmic_bytes(my_ptr.numel() - 1, my_col.numel(), args.feat, elem))],
+                                   device=device, dtype=torch.float64)
+        every_bytes = torch.empty(world, device=device, dtype=torch.float64)
+        dist.all_gather_into_tensor(every_bytes, shard_bytes)
+        if isinstance(sharded, StagedHaloSpmm):
+            sharded.timing = True
+            barrier()
+            step()
+            barrier()
+            names = list(sharded.phase_ms().keys())
+            mine = torch.tensor(list(sharded.phase_ms().values()), device=device)
+            sharded.timing = False
+            dist.all_reduce(mine, op=dist.ReduceOp.MAX)
+            sharding["phases_ms"] = {n: round(float(v), 3) for n, v in zip(names, mine.tolist())}
+            sharding["phases_note"] = ("one step after the timed region: ms from the step's start to the END of each phase, "
+                                       "max over ranks; pack/exchange run on the side stream, product on the main stream")
 
+    launches_per_step = 2
+    if distributed and args.exchange.startswith("staged"):
+        peers = world - 1 if args.exchange == "staged_push" else 1
+        launches_per_step = len(sharded.stage_ptr) * (2 + 2 * peers)   # (pack gathers + product) x (kernel + fix-up)
+    elif distributed and args.exchange == "halo":
+        launches_per_step = 4
+    elif distributed and args.exchange == "pull":
+        launches_per_step = 2 * world
     result = {
         "metric": "spmm_sum_nnz_feat_per_s", "value": nnz * args.feat / (ms_per_step * 1e-3), "unit": "nnz*feat/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32" if elem == 4 else "bf16",
-        "data": "synthetic", "config": config, "clocks": clocks,
-        # ReduceKernel + FixupKernel per step on every rank (the plan is cached after warm-up); NCCL's kernels not counted
-        # (the halo step adds the pack gather, again ReduceKernel + FixupKernel; the pull step one gather per peer)
-        "gpu_launches": args.steps * world * (2 if not distributed or args.exchange == "allgather"
-                                              else 4 if args.exchange == "halo" else 2 * world),
+        "data": "synthetic", "config": config, "sharding": sharding, "clocks": clocks, "parity_check": parity,
+        # ReduceKernel + FixupKernel per product and per pack gather on every rank (plans are cached after warm-up);
+        # NCCL's own kernels are not counted
+        "gpu_launches": args.steps * world * launches_per_step,
     }
+
+    peaks = {}
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as handle:
+            peaks = json.load(handle)
+    except OSError:
+        pass
+    peak = float(peaks.get("hbm_gbs", 6650.0))
+    shape = "4,2" if elem == 4 else "8,1"
+    kernel = f"opsgnn::ReduceKernel<{args.dtype},{args.dtype},int64,int64,{shape},sum,lean,bulk>"
     if resident_ms is not None:
         result["x_resident"] = {"ms_per_step": resident_ms, "value": nnz * args.feat / (resident_ms * 1e-3),
                                 "per_rank_ms": resident_per_rank,
-                                "note": "local SpMM only, X already replicated (no all-gather in the step)"}
-
-    if rank == 0:
-        peaks = {}
-        try:
-            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as handle:
-                peaks = json.load(handle)
-        except OSError:
-            pass
-        peak = float(peaks.get("hbm_gbs", 6650.0))
-        if not distributed:
-            total = algorithmic_bytes(nodes, nnz, args.feat, elem)
-            achieved = total / (ms_per_step * 1e-3) / 1e9
-            shape = "4,2" if elem == 4 else "8,1"
-            result["roofline"] = {
-                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": NCU_DRAM_TRAFFIC.get(config["workload"]),
-                "peak_source": "measured" if peaks else "fallback", "algorithmic_bytes_per_launch": total,
-                "kernel": f"opsgnn::ReduceKernel<{args.dtype},{args.dtype},int64,int64,{shape},sum,lean,bulk> "
-                          "(+ FixupKernel, 0.8 % of the step, inside the same timed region)",
-            }
+                                "note": "local SpMM only, X already in place (no exchange in the step)"}
+        per_rank = [b / (ms * 1e-3) / 1e9 for b, ms in zip(every_bytes.tolist(), every_ms.tolist())]
+        result["roofline"] = {
+            "bound": "hbm", "achieved": min(per_rank), "peak": peak, "unit": "GB/s", "frac": min(per_rank) / peak,
+            "traffic": None, "peak_source": "measured" if peaks else "fallback",
+            "per_rank_achieved": [round(v, 1) for v in per_rank], "per_rank_frac": [round(v / peak, 3) for v in per_rank],
+            "kernel": kernel + " of every rank's local product, timed alone (x_resident); achieved = the slowest rank's "
+                      "algorithmic bytes / its time",
+        }
+    elif rank == 0:
+        total = algorithmic_bytes(nodes, nnz, args.feat, elem)
+        achieved = total / (ms_per_step * 1e-3) / 1e9
+        result["roofline"] = {
+            "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": NCU_DRAM_TRAFFIC.get(config["workload"]),
+            "peak_source": "measured" if peaks else "fallback", "algorithmic_bytes_per_launch": total,
+            "kernel": kernel + " (+ FixupKernel, 0.8 % of the step, inside the same timed region)",
+        }
 
     # ---- end to end through the public API with host buffers -----------------------------------------------------------
-    host_inputs = None
     out = None
     torch.cuda.empty_cache()
     if not args.no_e2e:
         if distributed:
+            del sharded, local_x, x_block
+            torch.cuda.empty_cache()
             result["e2e"] = end_to_end_sharded(args, host_shard, nnz, dist, device, world)
         else:
-            result["e2e"], host_inputs = end_to_end(args, csr_spmm, rowptr, col, value, x, nnz)
+            result["e2e"] = end_to_end(args, csr_spmm, rowptr, col, value, x, nnz)[0]
 
     if rank == 0 and not distributed and not args.no_cpu:
-        if host_inputs is None:
-            host_inputs = [t.cpu() for t in (rowptr, col, value, x)]
-        del rowptr, col, value, x
-        *host, x_host = host_inputs
-        sample_ptr, sample_col, sample_val, first, last = cpu_sample(*host, x_host, 1 << 22)
-        seconds, threads = time_cpu(sample_ptr, sample_col, sample_val.float(), x_host.float(), repeats=3)
+        seconds, threads = time_cpu(sample, repeats=3)
         result["cpu_baseline"] = {
-            "value": sample_col.numel() * args.feat / seconds, "unit": "nnz*feat/s", "cores": threads, "kind": "port",
-            "sample": f"rows [{first}, {last}) of the same graph: {sample_col.numel()} edges, best of 3 runs of "
+            "value": sample["edges"] * args.feat / seconds, "unit": "nnz*feat/s", "cores": threads, "kind": "port",
+            "sample": f"rows [{sample['first']}, {sample['last']}) of the same graph ({sample['edges']} edges, columns "
+                      f"relabelled to the {sample['x'].size(0)} rows of X they reference), best of 3 runs of "
                       f"oracle.spmm.csr_spmm_sum_vectorised ({seconds:.3f} s each)",
         }
+
+    # ---- the other half of the metric: SDDMM nnz/s (config 3) and the GAT layer (config 5) -------------------------------
+    if rank == 0 and not distributed and not args.no_ops:
+        del rowptr, col, value, x, my_ptr, my_col, my_val
+        torch.cuda.empty_cache()
+        result["ops"] = other_operators(device, skip_cpu=args.no_cpu)
     if rank == 0:
         print(json.dumps(result))
     if distributed:
         dist.destroy_process_group()
     return 0
+
+
+def other_operators(device, skip_cpu):
+    """`sddmm_csr` dot on BASELINE config 3 and the GAT layer of config 5 at full size, by the functions of bench_ops.py
+    (5 warm + 20 timed launches each, one CUDA-event pair per launch, median)."""
+    import types
+
+    import bench_ops
+
+    report = bench_ops.Report(types.SimpleNamespace(warm=5, timed=20, no_cpu=skip_cpu), echo=False)
+    bench_ops.config3(report, device, 21)
+    torch.cuda.empty_cache()
+    bench_ops.config5(report, device, 21)
+    torch.cuda.empty_cache()
+    lines = {line["op"]: line for line in report.lines}
+    dot = lines["sddmm_csr_dot_u_v"]
+    summary = {
+        "sddmm_nnz_per_s": dot["metric"]["value"], "sddmm_ms": dot["ms_median"],
+        "sddmm_roofline": {"bound": "hbm", "achieved": dot["achieved_gbs"], "peak": dot["peak_gbs"], "unit": "GB/s",
+                           "frac": dot["frac"], "traffic": dot.get("traffic"),
+                           "algorithmic_bytes_per_launch": dot["algorithmic_bytes"],
+                           "note": "B (0.5 GB) stays in L2, so the algorithmic rate exceeds the DRAM rate"},
+        "sddmm_cpu_baseline": dot.get("cpu_baseline"),
+        "gat_layer_ms": {op: lines[op]["ms_median"] for op in lines if op.startswith("gat_")},
+        "lines": report.lines,
+    }
+    return summary
+
+
+def bind_near_gpu(local):
+    """Best effort: restrict this process to the CPUs of the NUMA node the GPU hangs off, so pinned host buffers
+    (first touch) land in the memory closest to its PCIe root.  Returns what was done, for the record."""
+    try:
+        props = torch.cuda.get_device_properties(local)
+        address = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{address}/numa_node") as handle:
+            node = int(handle.read().strip())
+        if node < 0:
+            return {"numa_node": None, "note": "the platform reports no NUMA node for the GPU"}
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as handle:
+            text = handle.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            low, _, high = part.partition("-")
+            cpus.update(range(int(low), int(high or low) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return {"numa_node": node, "note": "none of the node's CPUs is available to this process"}
+        os.sched_setaffinity(0, allowed)
+        return {"numa_node": node, "cpus": len(allowed)}
+    except (OSError, ValueError, AttributeError) as exc:
+        return {"numa_node": None, "note": f"not bound: {type(exc).__name__}"}
+
+
+def copy_rates(pinned, staging, out_host, out_like, sync):
+    """GB/s of this rank's host -> device and device -> host copies: each direction alone, then both at once (what
+    the pipelined step does).  `sync()` lines the ranks up before each probe, so the rates are those of all ranks
+    copying at the same time."""
+    up_bytes = sum(t.numel() * t.element_size() for t in pinned)
+    down_bytes = out_host.numel() * out_host.element_size()
+    side = torch.cuda.Stream()
+    rates = {}
+
+    def timed(upload, download):
+        sync()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        main = torch.cuda.current_stream()
+        begin.record(main)
+        side.wait_event(begin)
+        if upload:
+            for dev, host in zip(staging, pinned):
+                dev.copy_(host, non_blocking=True)
+        if download:
+            with torch.cuda.stream(side):
+                out_host.copy_(out_like, non_blocking=True)
+        main.wait_stream(side)
+        end.record(main)
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end) * 1e-3
+
+    rates["h2d_alone_gbs"] = up_bytes / timed(True, False) / 1e9
+    rates["d2h_alone_gbs"] = down_bytes / timed(False, True) / 1e9
+    both = timed(True, True)
+    rates["both_directions_gbs"] = (up_bytes + down_bytes) / both / 1e9
+    rates["both_directions_ms"] = both * 1e3
+    return rates
 
 
 def host_available_bytes():
@@ -516,6 +707,20 @@ def end_to_end_sharded(args, pinned, nnz, dist, device, world):
         torch.cuda.synchronize()
 
     steps = max(3, min(args.steps, 5))
+    # what bounds the leg: this rank's copy rates with every rank copying at once, and the device part of a step alone
+    rates = copy_rates(pinned, like, out_host, torch.empty((rows, args.feat), dtype=dtype, device=device), barrier)
+    for dev, host in zip(like, pinned):
+        dev.copy_(host)
+    barrier()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    product(like)
+    begin.record()
+    product(like)
+    end.record()
+    barrier()
+    rates["device_part_ms"] = begin.elapsed_time(end)
+    gathered_rates = [None] * world
+    dist.all_gather_object(gathered_rates, {k: round(v, 2) for k, v in rates.items()})
     local_ms = run_pipelined(pinned, like, product, out_host, steps, barrier)
     del like
     elapsed = torch.tensor([local_ms * steps], device=device)
@@ -529,34 +734,38 @@ def end_to_end_sharded(args, pinned, nnz, dist, device, world):
             "h2d_bytes_per_step": int(in_bytes.item()), "d2h_bytes_per_step": int(out_bytes.item()),
             "api": "ops_gnn.distributed.RowShardedSpmm", "shard_row_cost": args.e2e_row_cost, "rows_rank0": rows,
             "overlap": "upload of step k+1 runs beside product and download of step k (2 staging sets, 3 streams)",
-            "note": "bytes are summed over ranks; time is the max over ranks"}
+            "note": "bytes are summed over ranks; time is the max over ranks",
+            "per_rank": gathered_rates,
+            "per_rank_note": "GB/s of each rank's pinned-host copies with all ranks copying at once (each direction alone, "
+                             "then both), and the device part of one step (validate + plan + all-gather + product); a "
+                             "step cannot be shorter than both_directions_ms of the slowest rank",
+            "host_binding": args.host_binding}
 
 
 def reference_arm(args, rowptr, col, value, x, config):
     """The reference's CPU algorithm (oracle port of its vectorised golden) on the host cores, same metric."""
-    host = [t.cpu() for t in (rowptr, col, value)]
-    x_host = x.float().cpu()
+    sample = row_sample(rowptr, col, value, lambda ids: x[ids], SAMPLE_EDGES)
     del rowptr, col, value, x
-    sample_ptr, sample_col, sample_val, first, last = cpu_sample(*host, x_host, 1 << 22)
-    sample_val = sample_val.float()
+    torch.cuda.empty_cache()
     from oracle.spmm import csr_spmm_sum_vectorised
 
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
+    operands = (sample["ptr"], sample["col"], sample["value"], sample["x"])
     for _ in range(max(args.warmup, 1)):
-        csr_spmm_sum_vectorised(sample_ptr, sample_col, sample_val, x_host)
+        csr_spmm_sum_vectorised(*operands)
     begin = time.perf_counter()
     for _ in range(args.steps):
-        csr_spmm_sum_vectorised(sample_ptr, sample_col, sample_val, x_host)
+        csr_spmm_sum_vectorised(*operands)
     seconds = (time.perf_counter() - begin) / args.steps
-    rate = sample_col.numel() * args.feat / seconds
-    sample = (f"each step = rows [{first}, {last}) of the graph ({sample_col.numel()} edges) through "
-              f"oracle.spmm.csr_spmm_sum_vectorised")
+    rate = sample["edges"] * args.feat / seconds
+    text = (f"each step = rows [{sample['first']}, {sample['last']}) of the graph ({sample['edges']} edges, columns "
+            f"relabelled to the {sample['x'].size(0)} rows of X they reference) through oracle.spmm.csr_spmm_sum_vectorised")
     print(json.dumps({
         "impl": "reference", "metric": "spmm_sum_nnz_feat_per_s", "value": rate, "unit": "nnz*feat/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": seconds * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
-        "cpu_baseline": {"value": rate, "unit": "nnz*feat/s", "cores": threads, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": rate, "unit": "nnz*feat/s", "cores": threads, "kind": "port", "sample": text},
         "e2e": {"value": rate, "unit": "nnz*feat/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }))

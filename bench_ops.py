@@ -69,9 +69,18 @@ def time_cpu(fn, repeats=3):
     return best
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch from an ncu capture of the same call (profiler figures copied
+# here, not measured by this script; the captures are summarised under profiles/)
+NCU_DRAM_TRAFFIC = {"sddmm_csr_dot_u_v": 3.2e9}
+
+
 class Report:
-    def __init__(self, args):
+    """Times one public call and prints (echo) or collects (lines) its JSON record."""
+
+    def __init__(self, args, echo=True):
         self.args = args
+        self.echo = echo
+        self.lines = []
         self.peak, self.peak_source = measured_peak()
 
     def emit(self, op, config, fn, nbytes, metric=None, cpu=None):
@@ -80,6 +89,8 @@ class Report:
                 "achieved_gbs": nbytes / (median * 1e-3) / 1e9, "peak_gbs": self.peak, "peak_source": self.peak_source,
                 "launches_timed": self.args.timed}
         line["frac"] = line["achieved_gbs"] / self.peak
+        if op in NCU_DRAM_TRAFFIC:
+            line["traffic"] = NCU_DRAM_TRAFFIC[op]
         if metric:
             name, units = metric
             line["metric"] = {"name": name, "value": units / (median * 1e-3)}
@@ -87,7 +98,9 @@ class Report:
             seconds, units, what = cpu()
             line["cpu_baseline"] = {"value": units / seconds, "unit": (metric[0] if metric else "units/s"),
                                     "cores": os.cpu_count() or 1, "kind": "port", "sample": what}
-        print(json.dumps(line), flush=True)
+        self.lines.append(line)
+        if self.echo:
+            print(json.dumps(line), flush=True)
 
 
 # ---- config 2: segment / scatter reductions and grouped softmax ------------------------------------------------------------

@@ -41,7 +41,7 @@ def test_spmm_copy_fixtures():
         if c["reduce"] in ("max", "min"):
             assert_same(got, c["out"], what)
         else:
-            assert_close(got, c["out"], what=what, scale=4.0)
+            assert_close(got, c["out"], what=what)
 
 
 def test_sddmm_fixtures():
@@ -82,8 +82,14 @@ def test_scatter_fixtures():
             assert_same(out, c["out"], what)
             assert_same(arg, c["arg"], what + " arg")
         elif c["src"].dtype.is_floating_point:
-            # the goldens add one element at a time in the value dtype; fp16/bf16 drift with the order
-            assert_close(out, c["out"], what=what, scale=20.0 if c["reduce"] == "mul" else 8.0)
+            # the goldens add one element at a time in the value dtype; fp16/bf16 sums drift with the order, so sums
+            # and means are bounded by the magnitude that was summed
+            magnitude = None
+            if c["reduce"] != "mul":
+                start = None if c["out_in"] is None else c["out_in"].double().abs()
+                magnitude = oracle.scatter_oracle(c["src"].double().abs(), c["index"], c["dim"], start, c["dim_size"],
+                                                  c["reduce"])
+            assert_close(out, c["out"], what=what, magnitude=magnitude)
         else:
             assert_same(out, c["out"], what)
 
@@ -91,15 +97,15 @@ def test_scatter_fixtures():
 def test_grouped_softmax_fixtures():
     for i, c in enumerate(load_golden("grouped_softmax")):
         args = (c["src"], c["index"], c["dim"], c["dim_size"])
-        assert_close(oracle.grouped_softmax_oracle(*args), c["softmax"], torch.float64, f"case {i} softmax", 1e3)
+        assert_close(oracle.grouped_softmax_oracle(*args), c["softmax"], torch.float64, f"case {i} softmax")
         assert_close(oracle.grouped_softmax_oracle(*args, log=True), c["log_softmax"], torch.float64,
-                     f"case {i} log_softmax", 1e3)
-        assert_close(oracle.grouped_logsumexp_oracle(*args), c["logsumexp"], torch.float64, f"case {i} logsumexp", 1e3)
+                     f"case {i} log_softmax")
+        assert_close(oracle.grouped_logsumexp_oracle(*args), c["logsumexp"], torch.float64, f"case {i} logsumexp")
 
 
 def test_segment_logsumexp_fixtures():
     for i, c in enumerate(load_golden("segment_logsumexp")):
-        assert_close(oracle.segment_logsumexp_oracle(c["src"], c["indptr"]), c["out"], torch.float64, f"case {i}", 1e3)
+        assert_close(oracle.segment_logsumexp_oracle(c["src"], c["indptr"]), c["out"], torch.float64, f"case {i}")
 
 
 def test_convert_fixtures():
@@ -183,4 +189,4 @@ def test_vectorised_baseline_equals_oracle():
     assert c["reduce"] == "sum" and c["mat"].dim() == 2
     want, _ = oracle.csr_spmm_oracle(c["ptr"], c["col"], c["value"], c["mat"], "sum")
     got = csr_spmm_sum_vectorised(c["ptr"], c["col"], c["value"], c["mat"], edge_chunk=97)
-    assert_close(got, want, what="vectorised baseline", scale=20.0)
+    assert_close(got, want, what="vectorised baseline")

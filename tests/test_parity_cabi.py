@@ -43,7 +43,7 @@ def test_csr_reduce_entry_point(cuda_device):
     src = torch.randn(int(ptr[-1]), 16, generator=gen)
     got, _ = _cabi.csr_reduce(dev[0], None, None, src.to(cuda_device), _cabi.REDUCE_LOGSUMEXP,
                               extremum=_cabi.EXTREMUM_PROPAGATE_NAN)
-    assert_close(got, oracle.segment_logsumexp_oracle(src, ptr).float(), what="segment log-sum-exp", scale=4.0)
+    assert_close(got, oracle.segment_logsumexp_oracle(src, ptr).float(), what="segment log-sum-exp")
 
 
 def test_sddmm_and_conversions_entry_points(cuda_device):
@@ -64,7 +64,7 @@ def test_sddmm_and_conversions_entry_points(cuda_device):
     out = torch.empty(nnz, device=cuda_device)
     _cabi.check(lib.opsgnn_sddmm_csr(ctypes.byref(desc), d_ptr.data_ptr(), d_col.data_ptr(), d_a.data_ptr(), d_b.data_ptr(),
                                      out.data_ptr(), workspace.data_ptr(), workspace.numel(), stream), "sddmm_csr")
-    assert_close(out, oracle.sddmm_oracle(ptr, col, a, b, "dot", "u", "v"), what="sddmm dot", scale=8.0)
+    assert_close(out, oracle.sddmm_oracle(ptr, col, a, b, "dot", "u", "v"), what="sddmm dot")
 
     rows = torch.repeat_interleave(torch.arange(3000), ptr[1:] - ptr[:-1])
     d_rows = rows.to(cuda_device)

@@ -23,8 +23,14 @@ def test_scatter_fixtures(cuda_device):
         else:
             out = ops_gnn.scatter(src, index, c["dim"], seed, c["dim_size"], c["reduce"])
             if c["src"].dtype.is_floating_point:
-                # the golden adds one element at a time in the value dtype; 16-bit sums drift with the order
-                assert_close(out, c["out"], what=what, scale=20.0 if c["reduce"] == "mul" else 8.0)
+                # the golden adds one element at a time in the value dtype: its 16-bit sums drift with the order, so
+                # sums and means are bounded by the magnitude that was summed (products by the product itself)
+                magnitude = None
+                if c["reduce"] != "mul":
+                    start = None if c["out_in"] is None else c["out_in"].double().abs()
+                    magnitude = oracle.scatter_oracle(c["src"].double().abs(), c["index"], c["dim"], start, c["dim_size"],
+                                                      c["reduce"])
+                assert_close(out, c["out"], what=what, magnitude=magnitude)
             else:
                 assert_same(out, c["out"], what)
         if seed is not None:
@@ -40,7 +46,7 @@ def test_scatter_compact_index_and_errors(cuda_device):
     d_src, d_index = src.to(cuda_device), index.to(cuda_device)
     for reduce in ("sum", "mean"):
         want = oracle.scatter_oracle(src.double(), index, 0, None, 700, reduce).float()
-        assert_close(ops_gnn.scatter(d_src, d_index, 0, None, 700, reduce), want, what=reduce, scale=8.0)
+        assert_close(ops_gnn.scatter(d_src, d_index, 0, None, 700, reduce), want, what=reduce)
     for reduce, fn in (("min", ops_gnn.scatter_min), ("max", ops_gnn.scatter_max)):
         out, arg = fn(d_src, d_index, 0, None, 700)
         want, want_arg = oracle.scatter_oracle(src, index, 0, None, 700, reduce)
@@ -56,6 +62,31 @@ def test_scatter_compact_index_and_errors(cuda_device):
         ops_gnn.scatter(src, index, 0, None, 700, "sum")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.float64])
+def test_scatter_extrema_negative_zero(cuda_device, dtype):
+    """-0.0 among negative and positive values: its bit pattern is INT_MIN as a signed integer, so an atomic extremum
+    that picks the integer view by `v >= 0` lets it beat every negative in a min and lose to everything in a max."""
+    import ops_gnn
+
+    src = torch.tensor([-5.0, -0.0, 3.0, -0.0, -1.0, -0.0, 0.0, -2.0, -0.0, -0.0, 2.0, -0.0], dtype=dtype)
+    index = torch.tensor([0, 0, 0, 1, 1, 2, 2, 3, 3, 4, 4, 5])
+    for order in (torch.arange(12), torch.arange(11, -1, -1)):       # both arrival orders
+        s, i = src[order], index[order]
+        for reduce, fn in (("min", ops_gnn.scatter_min), ("max", ops_gnn.scatter_max)):
+            out, arg = fn(s.to(cuda_device), i.to(cuda_device), 0, None, 7)
+            want, want_arg = oracle.scatter_oracle(s, i, 0, None, 7, reduce)
+            assert_same(out, want, f"{reduce} {dtype}")               # == treats the two zeros as equal, as torch does
+            assert_same(arg, want_arg, f"{reduce} {dtype} arg")
+    big = torch.where(torch.rand(20000, 8, generator=torch.Generator().manual_seed(3)) < 0.3,
+                      torch.tensor(-0.0), -torch.rand(20000, 8, generator=torch.Generator().manual_seed(4))).to(dtype)
+    where = torch.randint(0, 50, (20000,), generator=torch.Generator().manual_seed(5))
+    for reduce, fn in (("min", ops_gnn.scatter_min), ("max", ops_gnn.scatter_max)):
+        out, arg = fn(big.to(cuda_device), where.to(cuda_device), 0, None, 50)
+        want, want_arg = oracle.scatter_oracle(big, where, 0, None, 50, reduce)
+        assert_same(out, want, f"{reduce} {dtype} many")
+        assert_same(arg, want_arg, f"{reduce} {dtype} many arg")
+
+
 def test_grouped_fixtures(cuda_device):
     import ops_gnn
 
@@ -67,7 +98,7 @@ def test_grouped_fixtures(cuda_device):
             for labels in (index, index.to(torch.int32)):
                 got = fn(src, labels, c["dim"], c["dim_size"])
                 assert got.dtype == dtype
-                assert_close(got, c[name].to(dtype), what=f"case {i} {name} {dtype} {labels.dtype}", scale=4.0)
+                assert_close(got, c[name].to(dtype), what=f"case {i} {name} {dtype} {labels.dtype}")
 
 
 def test_config2_softmax_sorted_and_shuffled(cuda_device):
@@ -85,13 +116,12 @@ def test_config2_softmax_sorted_and_shuffled(cuda_device):
     for name, labels, values in (("sorted", index, src), ("shuffled", index[perm], src[perm])):
         d_src, d_index = values.to(cuda_device), labels.to(cuda_device)
         assert_close(ops_gnn.scatter_softmax(d_src, d_index, 0, groups),
-                     oracle.grouped_softmax_oracle(values, labels, 0, groups).float(), what=name + " softmax", scale=2.0)
+                     oracle.grouped_softmax_oracle(values, labels, 0, groups).float(), what=name + " softmax")
         assert_close(ops_gnn.scatter_log_softmax(d_src, d_index, 0, groups),
                      oracle.grouped_softmax_oracle(values, labels, 0, groups, log=True).float(),
-                     what=name + " log_softmax", scale=2.0)
+                     what=name + " log_softmax")
         assert_close(ops_gnn.scatter_logsumexp(d_src, d_index, 0, groups),
-                     oracle.grouped_logsumexp_oracle(values, labels, 0, groups).float(), what=name + " logsumexp",
-                     scale=2.0)
+                     oracle.grouped_logsumexp_oracle(values, labels, 0, groups).float(), what=name + " logsumexp")
 
 
 def test_grouped_gradients(cuda_device):
@@ -111,4 +141,4 @@ def test_grouped_gradients(cuda_device):
         fn(x, index.to(cuda_device), 0, 9).backward(up.to(cuda_device))
         x64 = src.double().requires_grad_(True)
         ref(x64).backward(up.double())
-        assert_close(x.grad, x64.grad.float(), what=fn.__name__ + " grad", scale=10.0)
+        assert_close(x.grad, x64.grad.float(), what=fn.__name__ + " grad")

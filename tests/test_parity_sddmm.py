@@ -21,9 +21,9 @@ def test_sddmm_fixtures(cuda_device):
             assert_same(got, c["out"], what)
         elif c["op"] == "dot":
             assert got.dtype == c["out"].dtype
-            assert_close(got, c["out"], what=what, scale=4.0)
+            assert_close(got, c["out"], what=what)
         else:
-            assert_close(got, c["out"], what=what, scale=1.0)
+            assert_close(got, c["out"], what=what)
 
 
 def test_rmat_dot(cuda_device):

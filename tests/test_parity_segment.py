@@ -27,7 +27,9 @@ def test_segment_csr_fixtures(cuda_device):
         else:
             out = ops_gnn.segment_csr(src, indptr, None, c["reduce"])
             if c["src"].dtype.is_floating_point:
-                assert_close(out, c["out"], what=what, scale=4.0)
+                # the golden accumulates in the value dtype: its bf16 sums are themselves a few bf16 roundings off
+                assert_close(out, c["out"], what=what,
+                             magnitude=oracle.segment_csr_oracle(c["src"].double().abs(), c["indptr"], c["reduce"]))
             else:
                 assert_same(out, c["out"], what)
 
@@ -49,7 +51,7 @@ def test_segment_coo_fixtures(cuda_device):
         else:
             out = ops_gnn.segment_coo(src, index, seed, c["dim_size"], c["reduce"])
             if c["src"].dtype.is_floating_point:
-                assert_close(out, c["out"], what=what, scale=4.0)
+                assert_close(out, c["out"], what=what)
             else:
                 assert_same(out, c["out"], what)
 
@@ -60,7 +62,7 @@ def test_segment_logsumexp_fixtures(cuda_device):
     for i, c in enumerate(load_golden("segment_logsumexp")):
         out = ops_gnn.segment_logsumexp(_gpu(c["src"], cuda_device), _gpu(c["indptr"], cuda_device))
         assert out.dtype == c["src"].dtype
-        assert_close(out, c["out"].to(c["src"].dtype), what=f"case {i} {c['src'].dtype}", scale=2.0)
+        assert_close(out, c["out"].to(c["src"].dtype), what=f"case {i} {c['src'].dtype}")
 
 
 def test_convert_fixtures(cuda_device):
@@ -98,8 +100,8 @@ def test_config2_segments(cuda_device, rows, feat):
     d_src, d_ptr, d_index = src.to(cuda_device), ptr.to(cuda_device), index.to(cuda_device)
     for reduce in ("sum", "mean"):
         want = oracle.segment_csr_oracle(src, ptr, reduce)
-        assert_close(ops_gnn.segment_csr(d_src, d_ptr, None, reduce), want, what="csr " + reduce, scale=4.0)
-        assert_close(ops_gnn.segment_coo(d_src, d_index, None, segments, reduce), want, what="coo " + reduce, scale=4.0)
+        assert_close(ops_gnn.segment_csr(d_src, d_ptr, None, reduce), want, what="csr " + reduce)
+        assert_close(ops_gnn.segment_coo(d_src, d_index, None, segments, reduce), want, what="coo " + reduce)
     for reduce, csr, coo in (("min", ops_gnn.segment_min_csr, ops_gnn.segment_min_coo),
                              ("max", ops_gnn.segment_max_csr, ops_gnn.segment_max_coo)):
         want, want_arg = oracle.segment_csr_oracle(src, ptr, reduce, return_arg=True)
@@ -107,7 +109,7 @@ def test_config2_segments(cuda_device, rows, feat):
             assert_same(got[0], want, f"{name} {reduce}")
             assert_same(got[1], want_arg, f"{name} {reduce} arg")
     assert_close(ops_gnn.segment_logsumexp(d_src, d_ptr), oracle.segment_logsumexp_oracle(src, ptr).float(),
-                 what="segment_logsumexp", scale=2.0)
+                 what="segment_logsumexp")
     assert_same(ops_gnn.ind2ptr(d_index, segments), ptr, "ind2ptr")
     assert_same(ops_gnn.ptr2ind(d_ptr, rows), index, "ptr2ind")
 
@@ -127,4 +129,4 @@ def test_one_long_segment(cuda_device):
     total = ops_gnn.segment_csr(d_src, d_ptr, None, "sum")
     exact = src.double().sum(0, keepdim=True)
     assert float((total.cpu().double() - exact).abs().max()) <= 1e-5 * float(src.double().abs().sum(0).max())
-    assert_close(ops_gnn.segment_logsumexp(d_src, d_ptr), oracle.segment_logsumexp_oracle(src, ptr).float(), scale=2.0)
+    assert_close(ops_gnn.segment_logsumexp(d_src, d_ptr), oracle.segment_logsumexp_oracle(src, ptr).float())
