@@ -206,6 +206,8 @@ def parse():
                              "auto = staged")
     parser.add_argument("--stages", default="0.2,0.25,0.3,0.25",
                         help="staged exchanges: shares of a shard's work per stage, in row order")
+    parser.add_argument("--exchange-ctas", type=int, default=148,
+                        help="staged exchanges: thread blocks of the pack / push kernel that runs beside the products")
     parser.add_argument("--row-cost", type=float, default=6.0, help="N > 1: cost of one output row in edges (shard balance)")
     parser.add_argument("--e2e-row-cost", type=float, default=1.0,
                         help="N > 1: the same for the host-buffer leg (measured at 4 GPUs: 272 ms per step with 1, 310 with 50)")
@@ -307,7 +309,8 @@ def main():
                 if kind in ("staged", "staged_push"):
                     return StagedHaloSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device,
                                           stage_fractions=fractions, row_cost=args.row_cost,
-                                          transport="push" if kind == "staged_push" else "alltoall")
+                                          transport="push" if kind == "staged_push" else "alltoall",
+                                          exchange_ctas=args.exchange_ctas)
                 return HaloShardedSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device,
                                        transport="pull" if kind == "pull" else "alltoall")
 
@@ -332,6 +335,7 @@ def main():
             sharding["halo_rows_rank0"] = {"sent": sent, "received": received}
             if args.exchange.startswith("staged"):
                 sharding["stage_fractions"] = fractions
+                sharding["exchange_ctas"] = args.exchange_ctas
                 sharding["stage_halo_rows_rank0"] = sharded.halo_counts
             local_ptr, local_col, local_x = my_ptr, sharded.col, sharded.compact
         else:
@@ -426,8 +430,7 @@ def main():
 
     launches_per_step = 2
     if distributed and args.exchange.startswith("staged"):
-        peers = world - 1 if args.exchange == "staged_push" else 1
-        launches_per_step = len(sharded.stage_ptr) * (2 + 2 * peers)   # (pack gathers + product) x (kernel + fix-up)
+        launches_per_step = len(sharded.stage_ptr) * 3   # per stage: one gather (pack or push), ReduceKernel, FixupKernel
     elif distributed and args.exchange == "halo":
         launches_per_step = 4
     elif distributed and args.exchange == "pull":

@@ -242,6 +242,19 @@ OPSGNN_API int opsgnn_permute_values(const int64_t* perm, const void* value, voi
  * (python/ops_gnn/_grouped_softmax.py:67-79, python/ops_gnn/scatter.py:347-361).  index_type I32/I64. */
 OPSGNN_API int opsgnn_index_stats(const void* index, int index_type, int64_t n, int64_t* stats, void* stream);
 
+/* out[i, :] = src[index[i], :] for rows of `row_bytes` bytes (a multiple of 16; src and every segment base 16-byte
+ * aligned), with the output cut into `segments` (1..OPSGNN_GATHER_MAX_SEGMENTS) consecutive pieces: segment s holds
+ * the next segment_rows[s] output rows and starts at segment_out[s].  The segments may live in different buffers,
+ * another GPU's mapped memory included (the kernel writes with plain stores).  `segment_rows` and `segment_out` are
+ * HOST arrays read during the call.  At most `max_ctas` thread blocks run (0 = no cap beyond eight per SM): the
+ * kernel is the exchange step of the row-sharded SpMM, runs beside a product and is bound by NVLink, so a few dozen
+ * blocks are enough.  index_type I32/I64; indices are clamped into [0, src_rows).
+ * No counterpart in the reference, which is a single-device library (it has no exchange step). */
+#define OPSGNN_GATHER_MAX_SEGMENTS 16
+OPSGNN_API int opsgnn_gather_rows(const void* src, const void* index, int index_type, int64_t rows, int64_t src_rows,
+                                  int64_t row_bytes, int segments, const int64_t* segment_rows, void* const* segment_out,
+                                  int max_ctas, void* stream);
+
 /* ======================================================================== */
 /* scatter (unsorted index)                                                  */
 /* ======================================================================== */

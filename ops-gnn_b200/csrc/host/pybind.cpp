@@ -38,6 +38,10 @@ void BindSpmm(py::module_& m)
     m.def("gather_rows", &GatherRows, py::arg("x"), py::arg("index"), py::arg("unit_ptr"), py::arg("out"),
           "out[i] = x[index[i]] through the CSR engine (unit_ptr = 0..n); not part of the reference binding",
           py::call_guard<py::gil_scoped_release>());
+    m.def("gather_rows_into", &GatherRowsInto, py::arg("x"), py::arg("index"), py::arg("outs"), py::arg("max_ctas") = 0,
+          "outs[s][i] = x[index[start_s + i]] with a capped grid; the outputs may be views of a peer's mapped buffer; not "
+          "part of the reference binding",
+          py::call_guard<py::gil_scoped_release>());
     m.def("csr_spmm_into", &CsrSpmmInto, py::arg("ptr"), py::arg("col"), py::arg("value"), py::arg("x"), py::arg("out"),
           "out[r] = sum_e value[e] * x[col[e]] into a caller-provided contiguous [rows, K] view; not part of the reference "
           "binding",

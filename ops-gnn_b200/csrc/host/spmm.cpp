@@ -359,6 +359,46 @@ at::Tensor GatherRows(const at::Tensor& x, const at::Tensor& index, const at::Te
     return out;
 }
 
+// outs[s][i, :] = x[index[start_s + i], :]: the bounded-footprint row gather behind the exchange step of the sharded SpMM.
+// `outs` are contiguous [rows_s, K] matrices whose row counts add up to index.numel(); they may be views of a peer's
+// symmetric-memory buffer (the kernel writes them with plain stores).  `max_ctas` caps the grid (0 = no cap).
+void GatherRowsInto(const at::Tensor& x, const at::Tensor& index, const std::vector<at::Tensor>& outs, int64_t max_ctas)
+{
+    const char* api = "gather_rows_into";
+    TORCH_CHECK(!outs.empty() && outs.size() <= OPSGNN_GATHER_MAX_SEGMENTS, api, ": between 1 and ",
+                OPSGNN_GATHER_MAX_SEGMENTS, " output segments");
+    TORCH_CHECK(x.defined() && x.device().is_cuda() && index.defined() && index.device() == x.device(), api,
+                ": x and index must be CUDA tensors on one GPU");
+    TORCH_CHECK(x.dim() == 2 && x.is_contiguous(), api, ": x must be a contiguous matrix");
+    TORCH_CHECK(index.dim() == 1 && index.is_contiguous() &&
+                    (index.scalar_type() == at::kInt || index.scalar_type() == at::kLong),
+                api, ": index must be a contiguous int32/int64 vector");
+    const int64_t row_bytes = x.size(1) * static_cast<int64_t>(x.element_size());
+    TORCH_CHECK(row_bytes % 16 == 0, api, ": a row must be a multiple of 16 bytes");
+    std::vector<int64_t> counts;
+    std::vector<void*> bases;
+    int64_t total = 0;
+    for (const auto& out : outs) {
+        TORCH_CHECK(out.defined() && out.device().is_cuda() && out.dim() == 2 && out.is_contiguous() &&
+                        out.scalar_type() == x.scalar_type() && out.size(1) == x.size(1),
+                    api, ": every output must be a contiguous CUDA matrix of x's dtype and width");
+        TORCH_CHECK(!out.is_alias_of(x), api, ": an output must not alias x");
+        counts.push_back(out.size(0));
+        bases.push_back(out.data_ptr());
+        total += out.size(0);
+    }
+    TORCH_CHECK(total == index.numel(), api, ": the outputs must hold one row per index");
+    if (total == 0 || row_bytes == 0) {
+        return;
+    }
+    TORCH_CHECK(x.size(0) > 0, api, ": x has no rows");
+    c10::cuda::CUDAGuard guard(x.device());
+    CheckStatus(opsgnn_gather_rows(x.const_data_ptr(), index.const_data_ptr(), DtypeId(index.scalar_type(), api), total,
+                                   x.size(0), row_bytes, static_cast<int>(outs.size()), counts.data(), bases.data(),
+                                   static_cast<int>(max_ctas), CurrentStream(x)),
+                api);
+}
+
 // out[r, :] = sum_e value[e] * x[col[e], :] written into a caller-provided `out` (a row range of a larger matrix is
 // fine: any contiguous [rows, K] view).  The staged sharded SpMM produces its output stage by stage with this; the
 // structure is trusted (it was validated when the shard was built), so no validation pass runs here.

@@ -27,6 +27,7 @@ EXPORTS = (
     "opsgnn_csr_reduce_status", "opsgnn_set_status_sink", "opsgnn_set_wait_polls",
     "opsgnn_csr_integer_mean", "opsgnn_sddmm_workspace_bytes", "opsgnn_sddmm_csr", "opsgnn_sddmm_csr_static",
     "opsgnn_spmm_value_grad",
+    "opsgnn_gather_rows",
     "opsgnn_ind2ptr", "opsgnn_ptr2ind", "opsgnn_csr_validate", "opsgnn_permute_values", "opsgnn_index_stats",
     "opsgnn_scatter_workspace_bytes", "opsgnn_scatter",
     "opsgnn_grouped_workspace_bytes", "opsgnn_grouped_forward", "opsgnn_grouped_backward",
@@ -82,6 +83,8 @@ _PROTOTYPES = {
     "opsgnn_sddmm_csr_static": (c_int, [POINTER(SddmmDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "opsgnn_spmm_value_grad": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
                                        c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "opsgnn_gather_rows": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, POINTER(c_int64),
+                                   POINTER(c_void_p), c_int, c_void_p]),
     "opsgnn_ind2ptr": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
     "opsgnn_ptr2ind": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
     "opsgnn_csr_validate": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),

@@ -363,14 +363,18 @@ class StagedHaloSpmm:
     pack IS the transfer, no send buffer and no NCCL data path; stream-ordered one-element all-reduces mark "every
     peer's stage-k rows have landed" and, at the start of a step, "nobody still reads last step's buffers".
 
-    ``spmm_into(ptr, col, value, x, out)`` and ``gather_rows(x, index, unit_ptr, out)`` default to the CUDA kernels; the
-    CPU tests pass stand-ins.
+    The exchange kernel is the bounded row gather (``_pybind.gather_rows_into``): one launch per stage serves every
+    peer, and its grid is capped at ``exchange_ctas`` thread blocks, because it runs beside a product and is bound by
+    NVLink latency, not by the SMs (one block per SM moves what the link takes and leaves room for the product's blocks).
+
+    ``spmm_into(ptr, col, value, x, out)`` and ``gather_rows(x, index, outs, max_ctas)`` default to the CUDA kernels;
+    the CPU tests pass stand-ins.
     """
 
     def __init__(self, rowptr, col, value, bounds: Sequence[int], feat: int, dtype, device, group=None,
                  stage_fractions: Sequence[float] = (0.25, 0.25, 0.25, 0.25), row_cost: float = 4.0,
                  transport: str = "alltoall", spmm_into: Optional[Callable] = None,
-                 gather_rows: Optional[Callable] = None):
+                 gather_rows: Optional[Callable] = None, exchange_ctas: int = 148):
         import torch.distributed as dist
 
         self.dist, self.group = dist, group
@@ -380,6 +384,7 @@ class StagedHaloSpmm:
         if transport not in ("alltoall", "push"):
             raise ValueError("transport must be 'alltoall' or 'push'")
         self.transport, self.feat, self.dtype, self.device = transport, feat, dtype, device
+        self.exchange_ctas = int(exchange_ctas)
         self.bounds = [int(b) for b in bounds]
         self.own_first, own_last = self.bounds[self.rank], self.bounds[self.rank + 1]
         self.own_rows = own_last - self.own_first
@@ -430,7 +435,6 @@ class StagedHaloSpmm:
                           for k in range(stages)]
         self.stage_col = [self.col[cut[k]:cut[k + 1]] for k in range(stages)]
         self.stage_val = [None if value is None else value[cut[k]:cut[k + 1]] for k in range(stages)]
-        self.unit_ptr = [torch.arange(rows.numel() + 1, dtype=col.dtype, device=device) for rows in self.send_rows]
 
         total_rows = self.own_rows + self.halo_rows
         if transport == "push":
@@ -442,10 +446,13 @@ class StagedHaloSpmm:
             from . import _pybind
 
             spmm_into = spmm_into or _pybind.csr_spmm_into
-            gather_rows = gather_rows or _pybind.gather_rows
+            gather_rows = gather_rows or _pybind.gather_rows_into
         self.spmm_into, self.gather_rows = spmm_into, gather_rows
         on_gpu = device.type == "cuda"
-        self.comm_stream = torch.cuda.Stream(device) if on_gpu else None
+        # High priority: when a pack (or push) kernel and a product are both pending, free SM slots go to the exchange
+        # first, so the next stage's rows get on the wire while the current product computes.  Without it the small
+        # exchange kernels queue behind the product's thread blocks and the stages run one after the other (measured).
+        self.comm_stream = torch.cuda.Stream(device, priority=-1) if on_gpu else None
         self.timing = False       # set it to collect CUDA events per phase of the next step (see phase_ms)
         self._events = None
 
@@ -466,7 +473,7 @@ class StagedHaloSpmm:
         self.compact = buffer[:total_rows]
         self._flag = torch.zeros(1, dtype=torch.int32, device=device)
         # For every stage, tell each owner where in this rank's compact buffer its rows go; learn the same from the peers.
-        self._push = []           # per stage: list of (peer block, first row in it, rows of my block to send, unit ptr)
+        self._push = []           # per stage: where each peer wants this rank's rows, in the order of send_rows[k]
         for k, want in enumerate(self.want_splits):
             starts, at = [], self.halo_start[k]
             for count in want:
@@ -476,16 +483,12 @@ class StagedHaloSpmm:
             theirs = torch.empty_like(mine)
             dist.all_to_all_single(theirs, mine, group=self.group)
             theirs = [int(v) for v in theirs.tolist()]
-            plan, offset = [], 0
+            targets = []
             for peer, count in enumerate(self.give_splits[k]):
-                if peer != self.rank and count:
+                if count:                           # nobody asks itself, so the segments are exactly the peers' shares
                     block = self._handle.get_buffer(peer, (capacity, self.feat), self.dtype)
-                    rows = self.send_rows[k][offset:offset + count].contiguous()
-                    unit = torch.arange(count + 1, dtype=rows.dtype, device=device)
-                    plan.append((peer, block[theirs[peer]:theirs[peer] + count], rows, unit))
-                offset += count
-            plan.sort(key=lambda item: (item[0] - self.rank) % self.world)   # next rank first: no lockstep on one peer
-            self._push.append(plan)
+                    targets.append(block[theirs[peer]:theirs[peer] + count])
+            self._push.append(targets)
 
     def _stream_barrier(self) -> None:
         self.dist.all_reduce(self._flag, group=self.group)  # ordered on the current stream; no host wait
@@ -503,16 +506,14 @@ class StagedHaloSpmm:
     def _exchange_stage(self, k: int) -> None:
         halo = self.compact[self.halo_start[k]:self.halo_start[k + 1]]
         if self.transport == "push":
-            for _, target, rows, unit in self._push[k]:
-                self.gather_rows(self.own_block, rows, unit, target)
+            if self._push[k]:                       # one launch stores into every peer's buffer: all of them receive at once
+                self.gather_rows(self.own_block, self.send_rows[k], self._push[k], self.exchange_ctas)
             self._mark(f"pack{k}")
             self._stream_barrier()                  # every peer's stage-k rows have landed here too
         else:
-            if self.send_rows[k].numel():
-                packed = self.own_block.new_empty((self.send_rows[k].numel(), self.feat))
-                self.gather_rows(self.own_block, self.send_rows[k], self.unit_ptr[k], packed)
-            else:
-                packed = self.own_block.new_empty((0, self.feat))
+            packed = self.own_block.new_empty((self.send_rows[k].numel(), self.feat))
+            if packed.size(0):
+                self.gather_rows(self.own_block, self.send_rows[k], [packed], self.exchange_ctas)
             self._mark(f"pack{k}")
             self.dist.all_to_all_single(halo, packed, self.want_splits[k], self.give_splits[k], group=self.group)
         self._mark(f"exchange{k}")

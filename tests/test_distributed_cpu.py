@@ -112,7 +112,8 @@ def _staged_worker(rank, world, port, fractions, result_dir):
     op = StagedHaloSpmm(ptr, c, v, bounds, x.size(1), x.dtype, torch.device("cpu"), stage_fractions=fractions,
                         row_cost=1.0,
                         spmm_into=lambda p_, c_, v_, mat, out: out.copy_(csr_spmm_sum_vectorised(p_, c_, v_, mat)),
-                        gather_rows=lambda block, index, unit, out: out.copy_(block[index]))
+                        gather_rows=lambda block, index, outs, ctas: torch.cat(list(outs)).copy_(block[index])
+                        if len(outs) > 1 else outs[0].copy_(block[index]))
     out = op(x[bounds[rank]:bounds[rank + 1]])
     assert torch.equal(out, op(op.own_block))                    # producing the block in place skips the copy
     stage_bounds = staged_row_bounds(ptr, fractions, row_cost=1.0)

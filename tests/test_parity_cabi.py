@@ -74,3 +74,28 @@ def test_sddmm_and_conversions_entry_points(cuda_device):
     made_rows = torch.empty(nnz, dtype=torch.int64, device=cuda_device)
     _cabi.check(lib.opsgnn_ptr2ind(d_ptr.data_ptr(), 3000, made_rows.data_ptr(), nnz, stream), "ptr2ind")
     assert_same(made_rows, rows, "ptr2ind")
+
+
+def test_gather_rows_entry_point(cuda_device):
+    """opsgnn_gather_rows through ctypes: segmented outputs in separate buffers, both index dtypes, row widths from one
+    16-byte vector to beyond one 512-byte piece, capped and uncapped grids; bit-exact against an index_select."""
+    from ops_gnn import _cabi
+
+    lib = _cabi.load()
+    gen = torch.Generator().manual_seed(31)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for dtype, width in ((torch.float32, 256), (torch.float32, 4), (torch.bfloat16, 200), (torch.float16, 520), (torch.float32, 100)):
+        src = torch.randn(3000, width, generator=gen).to(dtype).to(cuda_device)
+        for index_dtype, cap in ((torch.int64, 0), (torch.int32, 8), (torch.int64, 1)):
+            index = torch.randint(0, 3000, (7001,), generator=gen).to(index_dtype).to(cuda_device)
+            counts = [0, 2500, 1, 0, 4500]
+            outs = [torch.full((n, width), 7, dtype=dtype, device=cuda_device) for n in counts]
+            rows = (ctypes.c_int64 * len(counts))(*counts)
+            bases = (ctypes.c_void_p * len(counts))(*[o.data_ptr() if o.numel() else None for o in outs])
+            _cabi.check(lib.opsgnn_gather_rows(src.data_ptr(), index.data_ptr(), _cabi.torch_dtype_id(index_dtype), 7001, 3000,
+                                               width * src.element_size(), len(counts), rows, bases, cap, stream), "gather_rows")
+            assert_same(torch.cat(outs), src[index.long()], f"gather {dtype} width {width} cap {cap}")
+    bad = (ctypes.c_int64 * 1)(5)
+    base = (ctypes.c_void_p * 1)(outs[1].data_ptr())
+    assert lib.opsgnn_gather_rows(src.data_ptr(), index.data_ptr(), _cabi.I64, 6, 3000, 400, 1, bad, base, 0, stream) == -1
+    assert lib.opsgnn_gather_rows(src.data_ptr(), index.data_ptr(), _cabi.I64, 5, 3000, 100, 1, bad, base, 0, stream) == -1
