@@ -250,6 +250,11 @@ def config5(report, device, scale):
     total = (nnz * (8 + 2 * heads * 4) + nodes * (8 + heads * 4) + 2 * nnz * heads * 4 + 2 * nnz * heads * 4 + nnz * 8
              + nnz * (8 + heads * 4 + row) + nodes * (8 + row))
     report.emit("gat_layer_composed", name, layer, total, ("nnz/s", nnz))
+    # the fused form: log-sum-exp of the logits from the edge list and the [N, H] halves, then the aggregation with the
+    # weights formed in the gather ring; no [E, H] tensor is written or read
+    fused_bytes = (nnz * (8 + 8 + heads * 4) + nodes * heads * 8) + (nnz * (8 + heads * 4 + row) + nodes * (8 + 2 * heads * 4 + row))
+    report.emit("gat_layer_fused", name, lambda: ops_gnn.gat_aggregate(indptr, indices, x, left, right, 0.2, edge_rows=rows),
+                fused_bytes, ("nnz/s", nnz))
 
 
 def main():

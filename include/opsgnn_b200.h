@@ -212,6 +212,44 @@ OPSGNN_API int opsgnn_sddmm_csr(const OpsgnnSddmmDesc* desc, const void* indptr,
 OPSGNN_API int opsgnn_sddmm_csr_static(const OpsgnnSddmmDesc* desc, const void* indptr, const void* indices,
                                        const void* lhs, const void* rhs, void* out, void* stream);
 
+/* ======================================================================== */
+/* Fused graph attention (no counterpart in the reference)                   */
+/* ======================================================================== */
+/*
+ * One GAT layer over a CSR graph without materialising any per-edge tensor:
+ *   logit[e, h] = leaky_relu(left[row(e), h] + right[col(e), h], negative_slope)
+ *   lse[r, h]   = log sum_{e in row r} exp(logit[e, h])            (-inf for a row without edges)
+ *   out[r, h, :] = sum_{e in row r} exp(logit[e, h] - lse[r, h]) * x[col(e), h, :]
+ * The reference has no such entry point: it composes the layer from sddmm_csr, leaky_relu, scatter_softmax and
+ * spmm / bspmm (python/ops_gnn/spmm.py:148-208, 283-289) and writes the [E, H] logits and weights (and, in the spmm
+ * fallback, the [E, H, D] messages) to memory.  Two calls: opsgnn_attention_lse (edge list + the [N, H] halves only),
+ * then opsgnn_attention_aggregate (the weighted bulk instance of the CSR engine, weights formed in the gather ring).
+ * fp32 only.  The aggregation needs heads * width a multiple of 256, heads a multiple of 4 and at most 21, width a
+ * multiple of 4 and 16-byte aligned right / x / out; other shapes return OPSGNN_ERR_UNSUPPORTED (compose the layer
+ * from the four operators instead).
+ */
+typedef struct OpsgnnAttentionDesc {
+    int64_t rows;      /* CSR rows (destination nodes)                        */
+    int64_t src_rows;  /* rows of right and x (source nodes)                  */
+    int64_t heads;     /* H                                                   */
+    int64_t width;     /* D: features per head                                */
+    int64_t nnz;       /* edges                                               */
+    float negative_slope;
+    int32_t index_type; /* OPSGNN_I32 / OPSGNN_I64: ptr, col and edge_rows    */
+    int32_t dtype;      /* OPSGNN_F32                                         */
+} OpsgnnAttentionDesc;
+
+OPSGNN_API int opsgnn_attention_lse_workspace_bytes(const OpsgnnAttentionDesc* desc, int64_t* bytes);
+/* lse[rows, H] from edge_rows[nnz] (the CSR row of every edge, i.e. ptr2ind of the pointers), col[nnz], left[rows, H],
+ * right[src_rows, H].  Deterministic: partial states of rows that span 32-edge chunks are folded in chunk order. */
+OPSGNN_API int opsgnn_attention_lse(const OpsgnnAttentionDesc* desc, const void* edge_rows, const void* col, const float* left,
+                                    const float* right, float* lse, void* workspace, int64_t workspace_bytes, void* stream);
+/* out[rows, H * D]; plan and workspace are those of opsgnn_csr_reduce for a descriptor with feat = H * D,
+ * value_width = H, fp32 in and out, sum (opsgnn_csr_plan_bytes / opsgnn_csr_reduce_workspace_bytes). */
+OPSGNN_API int opsgnn_attention_aggregate(const OpsgnnAttentionDesc* desc, const void* ptr, const void* col, const float* left,
+                                          const float* right, const float* lse, const void* x, void* out, const void* plan,
+                                          void* workspace, int64_t workspace_bytes, void* stream);
+
 /* dvalue[e, w] = sum_b sum_k mat[b, col[e], k] * grad[b, row(e), k]  (w = 0 when width == 1, else k).
  * Replaces TorchSparseSpmmValueGrad (csrc/npu/torch_sparse_spmm/op_kernel/arch35/torch_sparse_spmm_kernel.h:326-395).
  * mean == 1 divides by the row's edge count.  grad and out are fp32; mat has dtype mat_type. */
@@ -255,6 +293,17 @@ OPSGNN_API int opsgnn_gather_rows(const void* src, const void* index, int index_
                                   int64_t row_bytes, int segments, const int64_t* segment_rows, void* const* segment_out,
                                   int max_ctas, void* stream);
 
+/* Batched row expansion, the inverse data movement of the segment reductions:
+ *   csr == 0: out[b, i, :] = src[b, index[b, i], :]                      index is [batches, out_rows] int64
+ *   csr == 1: out[b, i, :] = src[b, s, :] for ptr[b, s] <= i < ptr[b, s+1]  index is [batches, src_rows + 1] int64 pointers;
+ *             output rows before ptr[b, 0] are zero.
+ * src is [batches, src_rows, row_bytes], out is [batches, out_rows, row_bytes]; any element size (the copy unit is the
+ * largest power of two up to 16 bytes that divides the row and both base addresses).  An index outside [0, src_rows)
+ * writes zeros instead of reading out of range.  Replaces the GatherCoo launcher (csrc/npu/gather_coo/op_host/gather_coo.cpp)
+ * and the GatherCsr launcher (csrc/npu/gather_csr/op_host/gather_csr.cpp:262-330). */
+OPSGNN_API int opsgnn_gather_expand(const void* src, const int64_t* index, void* out, int64_t batches, int64_t src_rows,
+                                    int64_t out_rows, int64_t row_bytes, int csr, void* stream);
+
 /* ======================================================================== */
 /* scatter (unsorted index)                                                  */
 /* ======================================================================== */
@@ -297,10 +346,15 @@ typedef struct OpsgnnGroupedDesc {
     int64_t groups;  /* dim_size                              */
     int32_t mode;    /* OPSGNN_GROUPED_*                      */
     int32_t dtype;   /* F32 / F16 / BF16                      */
-    int32_t sorted;  /* 1: index is non-decreasing (enables the single-sweep path) */
+    int32_t sorted;  /* 0: any order (atomic phases); 1: index is non-decreasing (log-sum-exp sweep + apply sweep);   */
+                     /* OPSGNN_GROUPED_SORTED_SHORT: non-decreasing AND no group longer than                        */
+                     /* OPSGNN_GROUPED_SHORT_GROUP rows: softmax / log-softmax read src once (one batch, rows of     */
+                     /* whole 16-byte vectors; other shapes return OPSGNN_ERR_UNSUPPORTED, pass 1 for them)          */
     int32_t index_type; /* OPSGNN_I32 (what the reference binding passes) or OPSGNN_I64 */
 } OpsgnnGroupedDesc;
 
+#define OPSGNN_GROUPED_SORTED_SHORT 2
+#define OPSGNN_GROUPED_SHORT_GROUP 1024
 OPSGNN_API int opsgnn_grouped_workspace_bytes(const OpsgnnGroupedDesc* desc, int64_t* bytes);
 /* Replaces ScatterSoftmaxForward / ScatterLogSoftmaxForward / ScatterLogSumExpForward
  * (csrc/npu/scatter_softmax/op_kernel/common/scatter_softmax_kernel_entry.h:218-283) as launched by
@@ -309,6 +363,16 @@ OPSGNN_API int opsgnn_grouped_workspace_bytes(const OpsgnnGroupedDesc* desc, int
  * (logsumexp). */
 OPSGNN_API int opsgnn_grouped_forward(const OpsgnnGroupedDesc* desc, const void* src, const void* index, void* out,
                                       void* workspace, int64_t workspace_bytes, void* stream);
+/* Softmax / log-softmax over an UNSORTED index through a permutation: perm[dim_len] (int64) must order the rows by group
+ * (a stable argsort of index) and no group may hold more than OPSGNN_GROUPED_SHORT_GROUP rows.  Row perm[e] is read and
+ * written in place of row e of the sorted sequence, so the result lands in the caller's row order with one read of src,
+ * one write of out, no atomics and no fp32 scratch.  The workspace is that of the same descriptor with
+ * sorted = OPSGNN_GROUPED_SORTED_SHORT.  The reference runs its three atomic phases for every index
+ * (scatter_softmax_kernel_phase.h:126-279); this entry has no counterpart there.  One batch, rows of whole 16-byte
+ * vectors; other shapes and log-sum-exp return OPSGNN_ERR_UNSUPPORTED. */
+OPSGNN_API int opsgnn_grouped_forward_permuted(const OpsgnnGroupedDesc* desc, const void* src, const void* index,
+                                               const int64_t* perm, void* out, void* workspace, int64_t workspace_bytes,
+                                               void* stream);
 /* Replaces the backward launches (scatter_softmax_kernel_entry.h:247-264, 293-357; RunBackward
  * grouped_softmax_shared.h:212-248).  softmax: grad = out*(g - sum_group(out*g)); log_softmax:
  * grad = g - exp(out)*sum_group(g); logsumexp: grad = exp(src - out[group]) * g[group] (src required). */

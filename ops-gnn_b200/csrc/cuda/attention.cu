@@ -1,0 +1,284 @@
+// Fused graph-attention aggregation (GAT layer) in two launches, with no [E, H] tensor ever written:
+//
+//   logit[e, h] = leaky_relu(left[row(e), h] + right[col(e), h])
+//   lse[r, h]   = log sum_{e in row r} exp(logit[e, h])                                   (EdgeLogitLse + MergeBoundary)
+//   out[r, h, :] = sum_{e in row r} exp(logit[e, h] - lse[r, h]) * x[col(e), h, :]        (weighted bulk instance of the
+//                                                                                          CSR reduce engine, attention mode)
+//
+// The reference composes this layer from four operators and materialises the logits, the softmax weights and, in its
+// `spmm` fallback, the [E, H, D] messages (python/ops_gnn/spmm.py:148-208, 283-289 of the reference).  Here the first launch
+// reads only the edge list and the [N, H] halves (40 bytes per edge against 2 KiB per edge for the aggregation), the second
+// forms each weight from values that ride in the gather ring beside the row they scale.  Knowing the log-sum-exp before the
+// aggregation keeps every partial sum a plain sum: rows that span warps and thread blocks go through the engine's ordinary
+// carry path and the result is bitwise reproducible.
+//
+// EdgeLogitLse: the edge list is cut into chunks of kChunk consecutive edges; `heads` threads own a chunk (one head each)
+// and walk it in order with an online (maximum, scaled sum) state.  Rows that begin and end inside a chunk are finished
+// on the spot; the first and the last row of every chunk may continue in a neighbour, so their partial states go to a
+// boundary array that MergeBoundary folds in chunk order (one thread per head and run of equal rows: deterministic).
+// Algorithmic bytes: nnz * (row id + column id + H * 4) + rows * H * 8.
+#include "csr_instances.h"
+
+namespace opsgnn {
+namespace attention {
+
+constexpr int kThreads = 256;
+constexpr int kChunk = 32;
+
+struct LseParams {
+    const void* edge_rows;
+    const void* col;
+    const float* left;
+    const float* right;
+    float* lse;           // [rows, heads], pre-filled with -inf
+    int64_t* bound_row;   // [chunks, 2]: row of the chunk's first / last partial, -1 when absent
+    float* bound_state;   // [chunks, 2, heads, 2]: (maximum, sum)
+    int64_t nnz, rows, src_rows, chunks;
+    int heads, lanes;     // lanes = heads rounded up to a power of two
+    float slope;
+};
+
+__device__ __forceinline__ void Offer(float& m, float& s, float x)
+{
+    if (x > m) {
+        s = s * __expf(m - x) + 1.0f;  // m = -inf initially: 0 * 0 + 1
+        m = x;
+    } else {
+        s += __expf(x == m ? 0.0f : x - m);
+    }
+}
+
+template <class IndexT> __global__ void __launch_bounds__(kThreads) EdgeLogitLseKernel(const LseParams p)
+{
+    const int64_t thread = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    const int64_t chunk = thread / p.lanes;
+    const int head = static_cast<int>(thread - chunk * p.lanes);
+    if (chunk >= p.chunks || head >= p.heads) {
+        return;
+    }
+    const IndexT* __restrict__ edge_rows = static_cast<const IndexT*>(p.edge_rows);
+    const IndexT* __restrict__ col = static_cast<const IndexT*>(p.col);
+    const int64_t e0 = chunk * kChunk;
+    const int64_t e1 = (e0 + kChunk < p.nnz) ? e0 + kChunk : p.nnz;
+    const int64_t first_row = static_cast<int64_t>(__ldg(edge_rows + e0));
+    int64_t row = first_row;
+    float bias = __ldg(p.left + row * p.heads + head);
+    float m = -INFINITY, s = 0.0f;
+    bool first_done = false;
+    float* state = p.bound_state + (chunk * 2) * p.heads * 2 + head * 2;
+    for (int64_t base = e0; base < e1; base += 4) {
+        int64_t r[4], c[4];
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t e = base + u < e1 ? base + u : e1 - 1;
+            r[u] = static_cast<int64_t>(__ldg(edge_rows + e));
+            c[u] = static_cast<int64_t>(__ldg(col + e));
+            c[u] = c[u] < 0 ? 0 : (c[u] >= p.src_rows ? p.src_rows - 1 : c[u]);  // validated upstream; never fault
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            v[u] = __ldg(p.right + c[u] * p.heads + head);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (base + u >= e1) {
+                break;
+            }
+            if (r[u] != row) {  // the current row ends here
+                if (!first_done) {
+                    state[0] = m;  // first row of the chunk: may have begun in an earlier chunk
+                    state[1] = s;
+                    first_done = true;
+                } else if (row >= 0 && row < p.rows) {
+                    p.lse[row * p.heads + head] = s == 0.0f ? m : m + __logf(s);  // began and ended inside this chunk
+                }
+                row = r[u];
+                bias = (row >= 0 && row < p.rows) ? __ldg(p.left + row * p.heads + head) : 0.0f;
+                m = -INFINITY;
+                s = 0.0f;
+            }
+            float logit = bias + v[u];
+            logit = logit > 0.0f ? logit : logit * p.slope;
+            Offer(m, s, logit);
+        }
+    }
+    // the last row of the chunk may continue in the next one; a chunk with a single row has only a first partial
+    float* tail = state + p.heads * 2;
+    if (!first_done) {
+        state[0] = m;
+        state[1] = s;
+        tail[0] = -INFINITY;
+        tail[1] = 0.0f;
+    } else {
+        tail[0] = m;
+        tail[1] = s;
+    }
+    if (head == 0) {
+        p.bound_row[chunk * 2] = first_row;
+        p.bound_row[chunk * 2 + 1] = first_done ? row : -1;
+    }
+}
+
+// One thread per (boundary slot, head): the slot that opens a run of equal rows folds the run in slot order.
+__global__ void __launch_bounds__(kThreads) MergeBoundaryKernel(const LseParams p)
+{
+    const int64_t thread = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    const int64_t slot = thread / p.lanes;
+    const int head = static_cast<int>(thread - slot * p.lanes);
+    const int64_t slots = p.chunks * 2;
+    if (slot >= slots || head >= p.heads) {
+        return;
+    }
+    const int64_t row = p.bound_row[slot];
+    if (row < 0 || row >= p.rows) {
+        return;
+    }
+    int64_t before = slot - 1;  // nearest earlier slot that holds a partial
+    while (before >= 0 && p.bound_row[before] < 0) {
+        --before;
+    }
+    if (before >= 0 && p.bound_row[before] == row) {
+        return;  // not the opener of its run
+    }
+    float m = p.bound_state[(slot * p.heads + head) * 2];
+    float s = p.bound_state[(slot * p.heads + head) * 2 + 1];
+    for (int64_t next = slot + 1; next < slots; ++next) {
+        const int64_t other = p.bound_row[next];
+        if (other < 0) {
+            continue;
+        }
+        if (other != row) {
+            break;
+        }
+        csr::LseMerge(m, s, p.bound_state[(next * p.heads + head) * 2], p.bound_state[(next * p.heads + head) * 2 + 1]);
+    }
+    p.lse[row * p.heads + head] = s == 0.0f ? m : m + __logf(s);
+}
+
+__global__ void FillKernel(float* out, float value, int64_t n)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        out[i] = value;
+    }
+}
+
+inline int64_t Chunks(int64_t nnz) { return CeilDiv(nnz, kChunk); }
+
+inline bool CheckDesc(const OpsgnnAttentionDesc* d)
+{
+    return d != nullptr && d->rows >= 0 && d->src_rows >= 0 && d->nnz >= 0 && d->heads >= 1 && d->heads <= 32 && d->width >= 1 &&
+           (d->index_type == OPSGNN_I32 || d->index_type == OPSGNN_I64) && d->dtype == OPSGNN_F32;
+}
+
+}  // namespace attention
+}  // namespace opsgnn
+
+using namespace opsgnn;
+
+extern "C" int opsgnn_attention_lse_workspace_bytes(const OpsgnnAttentionDesc* desc, int64_t* bytes)
+{
+    if (!attention::CheckDesc(desc) || bytes == nullptr) {
+        return OPSGNN_ERR_INVALID;
+    }
+    const int64_t chunks = attention::Chunks(desc->nnz);
+    *bytes = AlignUp(chunks * 2 * 8, 256) + AlignUp(chunks * 2 * desc->heads * 2 * 4, 256);
+    return OPSGNN_OK;
+}
+
+extern "C" int opsgnn_attention_lse(const OpsgnnAttentionDesc* desc, const void* edge_rows, const void* col, const float* left,
+                                    const float* right, float* lse, void* workspace, int64_t workspace_bytes, void* stream)
+{
+    if (!attention::CheckDesc(desc)) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (desc->rows == 0) {
+        return OPSGNN_OK;
+    }
+    if (lse == nullptr || (desc->nnz > 0 && (edge_rows == nullptr || col == nullptr || left == nullptr || right == nullptr))) {
+        return OPSGNN_ERR_INVALID;
+    }
+    int64_t needed = 0;
+    opsgnn_attention_lse_workspace_bytes(desc, &needed);
+    if (desc->nnz > 0 && (workspace == nullptr || workspace_bytes < needed || !Aligned(workspace, 256))) {
+        return OPSGNN_ERR_WORKSPACE;
+    }
+    cudaStream_t s = AsStream(stream);
+    const int64_t cells = desc->rows * desc->heads;
+    int64_t fill_blocks = CeilDiv(cells, 256);
+    fill_blocks = fill_blocks < static_cast<int64_t>(SmCount()) * 8 ? fill_blocks : static_cast<int64_t>(SmCount()) * 8;
+    attention::FillKernel<<<static_cast<unsigned>(fill_blocks), 256, 0, s>>>(lse, -INFINITY, cells);  // rows without edges
+    if (desc->nnz == 0) {
+        return LaunchStatus();
+    }
+    attention::LseParams p{};
+    p.edge_rows = edge_rows;
+    p.col = col;
+    p.left = left;
+    p.right = right;
+    p.lse = lse;
+    p.nnz = desc->nnz;
+    p.rows = desc->rows;
+    p.src_rows = desc->src_rows;
+    p.chunks = attention::Chunks(desc->nnz);
+    p.heads = static_cast<int>(desc->heads);
+    p.lanes = 1;
+    while (p.lanes < p.heads) {
+        p.lanes <<= 1;
+    }
+    p.slope = desc->negative_slope;
+    char* cursor = static_cast<char*>(workspace);
+    p.bound_row = reinterpret_cast<int64_t*>(cursor);
+    cursor += AlignUp(p.chunks * 2 * 8, 256);
+    p.bound_state = reinterpret_cast<float*>(cursor);
+    const int64_t threads = p.chunks * p.lanes;
+    const unsigned grid = static_cast<unsigned>(CeilDiv(threads, attention::kThreads));
+    if (desc->index_type == OPSGNN_I64) {
+        attention::EdgeLogitLseKernel<int64_t><<<grid, attention::kThreads, 0, s>>>(p);
+    } else {
+        attention::EdgeLogitLseKernel<int32_t><<<grid, attention::kThreads, 0, s>>>(p);
+    }
+    const unsigned merge_grid = static_cast<unsigned>(CeilDiv(p.chunks * 2 * p.lanes, attention::kThreads));
+    attention::MergeBoundaryKernel<<<merge_grid, attention::kThreads, 0, s>>>(p);
+    return LaunchStatus();
+}
+
+extern "C" int opsgnn_attention_aggregate(const OpsgnnAttentionDesc* desc, const void* ptr, const void* col, const float* left,
+                                          const float* right, const float* lse, const void* x, void* out, const void* plan,
+                                          void* workspace, int64_t workspace_bytes, void* stream)
+{
+    if (!attention::CheckDesc(desc)) {
+        return OPSGNN_ERR_INVALID;
+    }
+    const int64_t feat = desc->heads * desc->width;
+    // The weighted bulk instance: 256-feature tiles of 16-byte vectors, a stage's column-side halves in its weight slot.
+    if (feat % 256 != 0 || (desc->heads * 4) % 16 != 0 || desc->width % 4 != 0 ||
+        (csr::kBulkStageBytes / 1024) * desc->heads * 4 > csr::kBulkWeightBytes) {
+        return OPSGNN_ERR_UNSUPPORTED;
+    }
+    if (desc->rows == 0) {
+        return OPSGNN_OK;
+    }
+    if (ptr == nullptr || out == nullptr || plan == nullptr || lse == nullptr || left == nullptr ||
+        (desc->nnz > 0 && (col == nullptr || right == nullptr || x == nullptr))) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (!Aligned(right, 16) || !Aligned(x, 16) || !Aligned(out, 16)) {
+        return OPSGNN_ERR_UNSUPPORTED;
+    }
+    OpsgnnCsrReduceDesc reduce{};
+    reduce.rows = desc->rows;
+    reduce.src_rows = desc->src_rows;
+    reduce.feat = feat;
+    reduce.nnz = desc->nnz;
+    reduce.batches = 1;
+    reduce.value_width = desc->heads;
+    reduce.reduce = OPSGNN_REDUCE_SUM;
+    reduce.ptr_type = desc->index_type;
+    reduce.col_type = desc->index_type;
+    reduce.in_type = OPSGNN_F32;
+    reduce.out_type = OPSGNN_F32;
+    return csr::RunAttention(reduce, ptr, col, left, right, lse, desc->negative_slope, x, out, plan, workspace, workspace_bytes,
+                             stream);
+}

@@ -123,10 +123,16 @@ extern "C" int opsgnn_csr_reduce_workspace_bytes(const OpsgnnCsrReduceDesc* desc
     return OPSGNN_OK;
 }
 
-extern "C" int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* ptr, const void* col, const void* val,
-                                 const void* mat, void* out, int64_t* arg, const void* plan, void* workspace,
-                                 int64_t workspace_bytes, void* stream)
+namespace opsgnn {
+namespace csr {
+
+// Argument checks and the launch parameters shared by opsgnn_csr_reduce and the attention aggregation.  Returns
+// OPSGNN_OK with *launch = false when there is nothing to compute.
+int PrepareReduce(const OpsgnnCsrReduceDesc* desc, const void* ptr, const void* col, const void* val, const void* mat,
+                  void* out, int64_t* arg, const void* plan, void* workspace, int64_t workspace_bytes, Params* params,
+                  bool* launch)
 {
+    *launch = false;
     int status = CheckDesc(desc);
     if (status != OPSGNN_OK) {
         return status;
@@ -135,6 +141,7 @@ extern "C" int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* pt
     if (d.rows == 0 || d.feat == 0) {
         return OPSGNN_OK;
     }
+    *launch = true;
     const int kind = KindOf(d.reduce);
     if (ptr == nullptr || out == nullptr || plan == nullptr || (d.nnz > 0 && mat == nullptr)) {
         return OPSGNN_ERR_INVALID;
@@ -157,7 +164,8 @@ extern "C" int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* pt
         return OPSGNN_ERR_WORKSPACE;
     }
 
-    Params p{};
+    Params& p = *params;
+    p = Params{};
     p.ptr = ptr;
     p.col = col;
     p.val = val;
@@ -194,6 +202,45 @@ extern "C" int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* pt
     cursor += AlignUp(p.num_cta * width * AccBytes(d.in_type), 256);
     p.carry_arg = reinterpret_cast<int64_t*>(cursor);
 
+    return OPSGNN_OK;
+}
+
+int RunAttention(const OpsgnnCsrReduceDesc& desc, const void* ptr, const void* col, const float* left, const float* right,
+                 const float* lse, float slope, const void* x, void* out, const void* plan, void* workspace,
+                 int64_t workspace_bytes, void* stream)
+{
+    Params p{};
+    bool launch = false;
+    // `right` stands in for the weight operand: one value per (source row, head) instead of one per (edge, head)
+    int status = PrepareReduce(&desc, ptr, col, right, x, out, nullptr, plan, workspace, workspace_bytes, &p, &launch);
+    if (status != OPSGNN_OK || !launch) {
+        return status;
+    }
+    p.attention = 1;
+    p.att_left = left;
+    p.att_right = right;
+    p.att_lse = lse;
+    p.att_slope = slope;
+    cudaStream_t s = AsStream(stream);
+    OPSGNN_CUDA_TRY(cudaMemsetAsync(p.status, 0, sizeof(unsigned long long), s));
+    return RunSpmmF32(p, desc.ptr_type == OPSGNN_I64, kSum, s);
+}
+
+}  // namespace csr
+}  // namespace opsgnn
+
+extern "C" int opsgnn_csr_reduce(const OpsgnnCsrReduceDesc* desc, const void* ptr, const void* col, const void* val,
+                                 const void* mat, void* out, int64_t* arg, const void* plan, void* workspace,
+                                 int64_t workspace_bytes, void* stream)
+{
+    Params p{};
+    bool launch = false;
+    int status = PrepareReduce(desc, ptr, col, val, mat, out, arg, plan, workspace, workspace_bytes, &p, &launch);
+    if (status != OPSGNN_OK || !launch) {
+        return status;
+    }
+    const OpsgnnCsrReduceDesc& d = *desc;
+    const int kind = KindOf(d.reduce);
     const bool index64 = d.ptr_type == OPSGNN_I64;
     cudaStream_t s = AsStream(stream);
     OPSGNN_CUDA_TRY(cudaMemsetAsync(p.status, 0, sizeof(unsigned long long), s));

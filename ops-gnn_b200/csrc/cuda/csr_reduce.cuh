@@ -75,6 +75,15 @@ struct Params {
     int64_t val_width;  // weights per edge
     int64_t val_group;  // wide == 2: consecutive features that share a weight (feat / val_width)
     int lanes_per_row;  // narrow instance: lanes that share one gathered row (a power of two below 32)
+    // Attention mode of the weighted bulk instance (fp32): the weight of edge e and feature group h is not read from
+    // `val` but formed from per-node halves, w = exp(leaky_relu(att_left[row, h] + att_right[col(e), h]) - att_lse[row, h]),
+    // i.e. the softmax over the row's edges given its log-sum-exp.  `att_right` rows (val_width values) are gathered
+    // into the weight slots of the ring by one more bulk copy per edge; att_left / att_lse are read once per row.
+    const float* att_left;
+    const float* att_right;
+    const float* att_lse;
+    float att_slope;
+    int attention;
 };
 
 // Self-checking build (-DOPSGNN_CHECKED): every global access of the reduce kernel is bounds-checked; a bad index is
@@ -262,7 +271,7 @@ constexpr int kBulkWarpBytes = kBulkStages * kBulkStageBytes;
 constexpr int kBulkSmemBytes = kWarps * kBulkWarpBytes + kWarps * kBulkStages * 8;
 // Per-group weights (one per edge and feature group, e.g. attention heads) ride along with the rows of a stage: the
 // weights of the stage's edges are contiguous in memory, so one more bulk copy per stage brings them in.
-constexpr int kBulkWeightBytes = 128;  // per stage: rows per stage x weights per edge x sizeof(T) must fit
+constexpr int kBulkWeightBytes = 256;  // per stage: rows per stage x weights per edge x sizeof(T) must fit
 constexpr int kBulkSmemBytesWeighted = kBulkSmemBytes + kWarps * kBulkStages * kBulkWeightBytes;
 // A failed try_wait may suspend the thread for up to this many nanoseconds (it wakes as soon as the phase completes),
 // so a waiting warp does not burn issue slots polling; the poll count bounds the wait to a few seconds in total, past
@@ -463,6 +472,7 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
                                                       ((GENERAL && BULK) ? warp * kBulkStages * kBulkWeightBytes : 0));
     const uint32_t weight_addr = (GENERAL && BULK) ? SharedAddress(weight_ring) : 0u;
     const uint32_t weight_row_bytes = static_cast<uint32_t>(p.val_width * static_cast<int64_t>(sizeof(T)));
+    constexpr bool kAttention = GENERAL && BULK && std::is_same<T, float>::value && RK == kSum;
     if constexpr (BULK && !kRingAsync) {
         if (lane == 0) {
 #pragma unroll
@@ -658,11 +668,17 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
         }
         const int n = (j1 - first < eb) ? j1 - first : eb;
         const int st = b % kBulkStages;
+        bool gather_weights = false;
+        if constexpr (kAttention) {
+            gather_weights = p.attention != 0;
+        }
         if (lane == 0) {
             if constexpr (GENERAL) {
                 MbarExpectTx(bar_addr + st * 8, static_cast<uint32_t>(n) * (seg_bytes + weight_row_bytes));
-                BulkLoad(weight_addr + static_cast<uint32_t>(st * kBulkWeightBytes), val + (a0 + first) * p.val_width,
-                         static_cast<uint32_t>(n) * weight_row_bytes, bar_addr + st * 8);
+                if (!gather_weights) {
+                    BulkLoad(weight_addr + static_cast<uint32_t>(st * kBulkWeightBytes), val + (a0 + first) * p.val_width,
+                             static_cast<uint32_t>(n) * weight_row_bytes, bar_addr + st * 8);
+                }
             } else {
                 MbarExpectTx(bar_addr + st * 8, static_cast<uint32_t>(n) * seg_bytes);
             }
@@ -681,9 +697,25 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
             if (OPSGNN_GUARD(4, static_cast<int64_t>(s_col[first + r]) * K + kbase + TILE - 1, p.src_rows * K + TILE)) {
                 BulkLoad(ring_addr + static_cast<uint32_t>(st * kBulkStageBytes + r * row_bytes),
                          mat + (static_cast<int64_t>(s_col[first + r]) * K32 + kbase), seg_bytes, bar_addr + st * 8);
+                if constexpr (kAttention) {
+                    if (gather_weights) {  // the column-side halves of this edge's logits, beside its row
+                        BulkLoad(weight_addr + static_cast<uint32_t>(st * kBulkWeightBytes) + static_cast<uint32_t>(r) * weight_row_bytes,
+                                 p.att_right + static_cast<int64_t>(s_col[first + r]) * p.val_width, weight_row_bytes,
+                                 bar_addr + st * 8);
+                    }
+                }
             }
         }
     };
+    // Attention mode: per-row constants of this lane's feature groups (row-side half of the logit, log-sum-exp).
+    float att_bias[NV];
+    float att_norm[NV];
+    int att_row = -1;
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        att_bias[v] = 0.0f;
+        att_norm[v] = 0.0f;
+    }
     int batch_id = 0;
     bool stalled = false;
     if constexpr (BULK) {
@@ -772,6 +804,13 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
                         if constexpr (GENERAL && BULK) {  // one weight per (edge, feature group), staged with the rows
                             w = Widen<A, T>(weight_ring[(batch_id % kBulkStages) * (kBulkWeightBytes / static_cast<int>(sizeof(T))) +
                                                         t * static_cast<int>(p.val_width) + static_cast<int>(group_of[v])]);
+                            if constexpr (kAttention) {
+                                if (p.attention) {  // staged value = column-side half of the logit
+                                    float logit = static_cast<float>(w) + att_bias[v];
+                                    logit = logit > 0.0f ? logit : logit * p.att_slope;
+                                    w = static_cast<A>(__expf(logit - att_norm[v]));
+                                }
+                            }
                         } else if constexpr (GENERAL) {
                             if (p.wide == 1) {
                                 wv = LoadGather<T, VEC>(val + (a0 + e) * K + koff[v]);
@@ -824,6 +863,17 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
             }                                                      \
             consume(std::integral_constant<int, N>{});             \
         }
+            if constexpr (kAttention) {
+                if (p.attention && t_end > t_begin && att_row != i) {  // first edges of a new row in this warp
+                    att_row = i;
+                    const int64_t at = (row0 + i) * p.val_width;
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) {
+                        att_bias[v] = __ldg(p.att_left + at + group_of[v]);
+                        att_norm[v] = __ldg(p.att_lse + at + group_of[v]);
+                    }
+                }
+            }
             if constexpr (RK == kLogSumExp && BULK) {
                 // The run sits in shared memory, so it is read twice: once for the maximum of the run, once for the
                 // sum of exponentials against the updated maximum.  One exponential and no branch per element; the

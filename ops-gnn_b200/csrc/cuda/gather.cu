@@ -73,10 +73,118 @@ __global__ void __launch_bounds__(kThreads) GatherRowsKernel(const Params p)
     }
 }
 
+// ---- gather_coo / gather_csr: batched row expansion ----------------------------------------------------------------------
+// out[b, i, :] = src[b, from(b, i), :] with from = index[b, i] (COO) or the segment s with ptr[b, s] <= i < ptr[b, s + 1]
+// (CSR; output rows before ptr[b, 0] are zero).  `lanes` lanes (a power of two) share one output row and move UNIT bytes
+// per lane and step, so a row of a few bytes does not idle a warp.  Algorithmic bytes: out rows * (index + 2 * row bytes).
+struct ExpandParams {
+    const unsigned char* src;
+    const int64_t* index;  // COO: [batches, out_rows]; CSR: [batches, segments + 1]
+    unsigned char* out;
+    int64_t batches, src_rows, out_rows, row_bytes;
+    int csr;    // 1: index holds segment pointers
+    int lanes;  // lanes per output row
+};
+
+template <class Unit> __global__ void __launch_bounds__(kThreads) ExpandRowsKernel(const ExpandParams p)
+{
+    const int lane = threadIdx.x & 31;
+    const int within = lane & (p.lanes - 1);
+    const int per_warp = 32 / p.lanes;
+    const int64_t warp = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * kWarps;
+    const int64_t total = p.batches * p.out_rows;
+    for (int64_t first = warp * per_warp; first < total; first += warps * per_warp) {
+        const int64_t row = first + lane / p.lanes;
+        if (row >= total) {
+            continue;
+        }
+        const int64_t b = row / p.out_rows;
+        const int64_t i = row - b * p.out_rows;
+        int64_t from;
+        if (p.csr) {
+            const int64_t* ptr = p.index + b * (p.src_rows + 1);
+            int64_t lo = 0, hi = p.src_rows + 1;  // first s with ptr[s] > i
+            while (lo < hi) {
+                const int64_t mid = (lo + hi) >> 1;
+                if (__ldg(ptr + mid) <= i) {
+                    lo = mid + 1;
+                } else {
+                    hi = mid;
+                }
+            }
+            from = lo - 1;  // -1: the row lies before ptr[0]; src_rows: beyond the last pointer (never, rows = endpoint)
+        } else {
+            from = __ldg(p.index + row);
+        }
+        const bool covered = from >= 0 && from < p.src_rows;
+        const Unit* source = reinterpret_cast<const Unit*>(p.src + (b * p.src_rows + (covered ? from : 0)) * p.row_bytes);
+        Unit* target = reinterpret_cast<Unit*>(p.out + row * p.row_bytes);
+        const int64_t units = p.row_bytes / static_cast<int64_t>(sizeof(Unit));
+        for (int64_t u = within; u < units; u += p.lanes) {
+            target[u] = covered ? __ldg(source + u) : Unit{};
+        }
+    }
+}
+
+template <class Unit> int LaunchExpand(ExpandParams p, cudaStream_t stream)
+{
+    const int64_t units = p.row_bytes / static_cast<int64_t>(sizeof(Unit));
+    int lanes = 1;
+    while (lanes < 32 && lanes < units) {
+        lanes <<= 1;
+    }
+    p.lanes = lanes;
+    const int64_t total = p.batches * p.out_rows;
+    int64_t ctas = CeilDiv(total, static_cast<int64_t>(kWarps) * (32 / lanes));
+    const int64_t cap = static_cast<int64_t>(SmCount()) * 16;
+    ctas = ctas < cap ? ctas : cap;
+    ExpandRowsKernel<Unit><<<static_cast<unsigned>(ctas), kThreads, 0, stream>>>(p);
+    return LaunchStatus();
+}
+
 }  // namespace gather
 }  // namespace opsgnn
 
 using namespace opsgnn;
+
+extern "C" int opsgnn_gather_expand(const void* src, const int64_t* index, void* out, int64_t batches, int64_t src_rows,
+                                    int64_t out_rows, int64_t row_bytes, int csr, void* stream)
+{
+    if (batches < 0 || src_rows < 0 || out_rows < 0 || row_bytes < 0) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (batches == 0 || out_rows == 0 || row_bytes == 0) {
+        return OPSGNN_OK;
+    }
+    if (out == nullptr || index == nullptr || (src_rows > 0 && src == nullptr)) {
+        return OPSGNN_ERR_INVALID;
+    }
+    gather::ExpandParams p{};
+    p.src = static_cast<const unsigned char*>(src);
+    p.index = index;
+    p.out = static_cast<unsigned char*>(out);
+    p.batches = batches;
+    p.src_rows = src_rows;
+    p.out_rows = out_rows;
+    p.row_bytes = row_bytes;
+    p.csr = csr ? 1 : 0;
+    cudaStream_t s = AsStream(stream);
+    const uintptr_t mix = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(out) | static_cast<uintptr_t>(row_bytes);
+    if (mix % 16 == 0) {
+        return gather::LaunchExpand<uint4>(p, s);
+    }
+    if (mix % 8 == 0) {
+        return gather::LaunchExpand<uint2>(p, s);
+    }
+    if (mix % 4 == 0) {
+        return gather::LaunchExpand<uint32_t>(p, s);
+    }
+    if (mix % 2 == 0) {
+        return gather::LaunchExpand<uint16_t>(p, s);
+    }
+    return gather::LaunchExpand<uint8_t>(p, s);
+}
 
 extern "C" int opsgnn_gather_rows(const void* src, const void* index, int index_type, int64_t rows, int64_t src_rows,
                                   int64_t row_bytes, int segments, const int64_t* segment_rows, void* const* segment_out,

@@ -6,7 +6,14 @@
 // pointers by a boundary scan, the CSR reduce engine computes one fp32 log-sum-exp per (batch, group, feature) in a
 // single sweep of src without atomics (online maximum + rescaled sum), and one more sweep writes
 // exp(x - lse) or x - lse.  src is read twice and out written once.
-// Forward, unsorted index: the reference's three phases on fp32 scratch of shape [batch, groups, after]:
+// Forward, short groups (softmax / log-softmax, one batch, rows of whole 16-byte vectors, every group at most
+// OPSGNN_GROUPED_SHORT_GROUP rows - the planner knows that from a cached fact about the index): SegmentSoftmaxKernel.
+// A group of lanes owns a whole group of rows: it reads the rows once (the first eight stay in registers, longer
+// groups come back from L1 / L2), forms the log-sum-exp online and writes exp(x - lse) or x - lse straight away, so src
+// crosses DRAM once and out once: the algorithmic bytes.  With a permutation (a stable argsort of an UNSORTED index,
+// made and cached by the planner) the same kernel reads and writes row perm[e] instead of row e: the unsorted case
+// then needs no atomics and no fp32 scratch either.
+// Forward, unsorted index without a permutation: the reference's three phases on fp32 scratch of shape [batch, groups, after]:
 // atomic maximum, atomic sum of exp(x - max), then normalise (or max + log(sum) per group for log-sum-exp).
 // Special values follow torch: a group holding +inf or only -inf gives NaN for softmax / log-softmax; log-sum-exp
 // gives +inf / -inf for those groups and -inf for a group without members; NaN spreads over its group.
@@ -161,12 +168,14 @@ template <class T> __global__ void __launch_bounds__(kThreads) FinishLogSumExpKe
 // ---- forward, sorted -------------------------------------------------------------------------------------------------
 // ptr[g] = number of index entries smaller than g (boundary scan of the sorted index).
 template <class IndexT>
-__global__ void BoundaryKernel(const IndexT* __restrict__ index, int64_t n, int64_t* __restrict__ ptr, int64_t groups)
+__global__ void BoundaryKernel(const IndexT* __restrict__ index, int64_t n, int64_t* __restrict__ ptr, int64_t groups,
+                               const int64_t* __restrict__ perm = nullptr)
 {
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
     for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e <= n; e += stride) {
-        int64_t prev = e == 0 ? -1 : static_cast<int64_t>(index[e - 1]);
-        int64_t cur = e == n ? groups : static_cast<int64_t>(index[e]);
+        // with a permutation the sorted sequence is index[perm[0]], index[perm[1]], ...
+        int64_t prev = e == 0 ? -1 : static_cast<int64_t>(index[perm != nullptr ? perm[e - 1] : e - 1]);
+        int64_t cur = e == n ? groups : static_cast<int64_t>(index[perm != nullptr ? perm[e] : e]);
         prev = prev < -1 ? -1 : (prev > groups ? groups : prev);
         cur = cur > groups ? groups : cur;
         for (int64_t g = prev + 1; g <= cur; ++g) {
@@ -242,6 +251,117 @@ template <class T, int VEC> __global__ void __launch_bounds__(kThreads) ApplyLse
     }
 }
 
+
+// ---- forward, short groups: one read of src, one write of out ---------------------------------------------------------
+// `lanes` lanes (a power of two) own one group of rows at a time and `VEC` consecutive features each; a row wider than
+// lanes * VEC features is walked tile by tile.  Row e of the (sorted) sequence is row perm[e] of src and out when a
+// permutation is given.  Pseudo groups `groups` and `groups + 1` are the rows whose label lies below 0 or at / above
+// `groups` (they come first / last in the sorted order): their output is 0, as in the other paths.
+constexpr int kCachedRows = 8;
+
+template <class T, int VEC> __global__ void __launch_bounds__(kThreads) SegmentSoftmaxKernel(
+    const Params p, const int64_t* __restrict__ ptr, const int64_t* __restrict__ perm, int lanes)
+{
+    const T* __restrict__ src = static_cast<const T*>(p.src);
+    T* __restrict__ out = static_cast<T*>(p.out);
+    const int lane = threadIdx.x & (lanes - 1);
+    const int64_t team = (static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x) / lanes;
+    const int64_t teams = static_cast<int64_t>(gridDim.x) * kThreads / lanes;
+    const int64_t vectors = p.after / VEC;
+    for (int64_t g = team; g < p.groups + 2; g += teams) {
+        const bool real = g < p.groups;
+        const int64_t first = real ? ptr[g] : (g == p.groups ? 0 : ptr[p.groups]);
+        const int64_t last = real ? ptr[g + 1] : (g == p.groups ? ptr[0] : p.dim_len);
+        for (int64_t tile = lane; tile < vectors; tile += lanes) {
+            const int64_t offset = tile * VEC;
+            if (!real) {
+                float zero[VEC];
+#pragma unroll
+                for (int c = 0; c < VEC; ++c) {
+                    zero[c] = 0.0f;
+                }
+                for (int64_t e = first; e < last; ++e) {
+                    const int64_t row = perm != nullptr ? perm[e] : e;
+                    StoreStream<T, VEC>(out + row * p.after + offset, Repack<T, float, VEC>(zero));
+                }
+                continue;
+            }
+            Pack<T, VEC> kept[kCachedRows];
+            float m[VEC], s[VEC];
+#pragma unroll
+            for (int c = 0; c < VEC; ++c) {
+                m[c] = -INFINITY;
+                s[c] = 0.0f;
+            }
+            // first sweep: online (maximum, scaled sum); the first kCachedRows rows stay in registers
+#pragma unroll
+            for (int k = 0; k < kCachedRows; ++k) {
+                if (first + k < last) {
+                    const int64_t row = perm != nullptr ? perm[first + k] : first + k;
+                    kept[k] = LoadGather<T, VEC>(src + row * p.after + offset);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kCachedRows; ++k) {
+                if (first + k < last) {
+                    float x[VEC];
+                    Unpack<float, T, VEC>(kept[k], x);
+#pragma unroll
+                    for (int c = 0; c < VEC; ++c) {
+                        if (x[c] > m[c]) {
+                            s[c] = s[c] * __expf(m[c] - x[c]) + 1.0f;
+                            m[c] = x[c];
+                        } else {
+                            s[c] += __expf(x[c] == m[c] ? 0.0f : x[c] - m[c]);
+                        }
+                    }
+                }
+            }
+            for (int64_t e = first + kCachedRows; e < last; ++e) {
+                const int64_t row = perm != nullptr ? perm[e] : e;
+                float x[VEC];
+                Unpack<float, T, VEC>(LoadGather<T, VEC>(src + row * p.after + offset), x);
+#pragma unroll
+                for (int c = 0; c < VEC; ++c) {
+                    if (x[c] > m[c]) {
+                        s[c] = s[c] * __expf(m[c] - x[c]) + 1.0f;
+                        m[c] = x[c];
+                    } else {
+                        s[c] += __expf(x[c] == m[c] ? 0.0f : x[c] - m[c]);
+                    }
+                }
+            }
+            float lse[VEC];
+#pragma unroll
+            for (int c = 0; c < VEC; ++c) {
+                lse[c] = s[c] == 0.0f ? m[c] : m[c] + __logf(s[c]);
+            }
+            // second sweep: the result; a group with a +inf member, only -inf members or a NaN is NaN throughout
+            auto finish = [&](const Pack<T, VEC>& packed, int64_t row) {
+                float x[VEC], y[VEC];
+                Unpack<float, T, VEC>(packed, x);
+#pragma unroll
+                for (int c = 0; c < VEC; ++c) {
+                    const float shifted = x[c] - lse[c];
+                    const float value = p.mode == OPSGNN_GROUPED_SOFTMAX ? __expf(shifted) : shifted;
+                    y[c] = isfinite(lse[c]) ? value : NAN;
+                }
+                StoreStream<T, VEC>(out + row * p.after + offset, Repack<T, float, VEC>(y));
+            };
+#pragma unroll
+            for (int k = 0; k < kCachedRows; ++k) {
+                if (first + k < last) {
+                    finish(kept[k], perm != nullptr ? perm[first + k] : first + k);
+                }
+            }
+            for (int64_t e = first + kCachedRows; e < last; ++e) {
+                const int64_t row = perm != nullptr ? perm[e] : e;
+                finish(LoadGather<T, VEC>(src + row * p.after + offset), row);
+            }
+        }
+    }
+}
+
 template <class T> __global__ void CastKernel(const float* __restrict__ in, T* __restrict__ out, int64_t n)
 {
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
@@ -311,7 +431,7 @@ inline Layout MakeLayout(const OpsgnnGroupedDesc& d)
     cursor += AlignUp(l.stats * 4, 256);
     l.total_off = cursor;
     cursor += AlignUp(l.stats * 4, 256);
-    if (d.sorted) {
+    if (d.sorted) {  // also the permuted form: the boundary scan runs over the sorted sequence
         l.ptr_off = cursor;
         cursor += AlignUp((d.groups + 1) * 8, 256);
         int64_t plan_bytes = 0;
@@ -337,17 +457,40 @@ inline Layout MakeLayout(const OpsgnnGroupedDesc& d)
     return l;
 }
 
-template <class T> int Forward(const OpsgnnGroupedDesc& d, Params p, char* workspace, const Layout& l, cudaStream_t s)
+template <class T> bool ShortGroupShape(const OpsgnnGroupedDesc& d, const Params& p)
+{
+    constexpr int kVec = 16 / sizeof(T);
+    return d.mode != OPSGNN_GROUPED_LOGSUMEXP && d.batch == 1 && d.after % kVec == 0 && Aligned(p.src, 16) && Aligned(p.out, 16);
+}
+
+template <class T>
+int Forward(const OpsgnnGroupedDesc& d, Params p, char* workspace, const Layout& l, cudaStream_t s, const int64_t* perm = nullptr)
 {
     const int64_t n = d.batch * d.dim_len * d.after;
     if (d.sorted && n > 0 && l.stats > 0) {
         int64_t* ptr = reinterpret_cast<int64_t*>(workspace + l.ptr_off);
         if (p.index64) {
             BoundaryKernel<int64_t><<<Grid(d.dim_len + 1), kThreads, 0, s>>>(static_cast<const int64_t*>(p.index), d.dim_len,
-                                                                         ptr, d.groups);
+                                                                         ptr, d.groups, perm);
         } else {
             BoundaryKernel<int32_t><<<Grid(d.dim_len + 1), kThreads, 0, s>>>(static_cast<const int32_t*>(p.index), d.dim_len,
-                                                                         ptr, d.groups);
+                                                                         ptr, d.groups, perm);
+        }
+        if (d.sorted == OPSGNN_GROUPED_SORTED_SHORT || perm != nullptr) {
+            if (!ShortGroupShape<T>(d, p)) {
+                return OPSGNN_ERR_UNSUPPORTED;
+            }
+            constexpr int kVec = 16 / sizeof(T);
+            const int64_t vectors = d.after / kVec;
+            int lanes = 1;
+            while (lanes < 32 && lanes < vectors) {
+                lanes <<= 1;
+            }
+            int64_t blocks = CeilDiv((d.groups + 2) * lanes, kThreads);
+            const int64_t cap = static_cast<int64_t>(SmCount()) * 32;
+            blocks = blocks < cap ? blocks : cap;
+            SegmentSoftmaxKernel<T, kVec><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p, ptr, perm, lanes);
+            return LaunchStatus();
         }
         int status = opsgnn_csr_plan_build(ptr, OPSGNN_I64, d.groups, d.dim_len, workspace + l.plan_off, s);
         if (status != OPSGNN_OK) {
@@ -487,6 +630,45 @@ extern "C" int opsgnn_grouped_forward(const OpsgnnGroupedDesc* desc, const void*
             return Forward<__half>(d, p, static_cast<char*>(workspace), l, s);
         default:
             return Forward<__nv_bfloat16>(d, p, static_cast<char*>(workspace), l, s);
+    }
+}
+
+extern "C" int opsgnn_grouped_forward_permuted(const OpsgnnGroupedDesc* desc, const void* src, const void* index,
+                                               const int64_t* perm, void* out, void* workspace, int64_t workspace_bytes,
+                                               void* stream)
+{
+    int status = CheckDesc(desc);
+    if (status != OPSGNN_OK) {
+        return status;
+    }
+    OpsgnnGroupedDesc d = *desc;
+    if (d.mode == OPSGNN_GROUPED_LOGSUMEXP) {
+        return OPSGNN_ERR_UNSUPPORTED;
+    }
+    d.sorted = OPSGNN_GROUPED_SORTED_SHORT;  // the sequence index[perm[.]] is sorted and its groups are short
+    const Layout l = MakeLayout(d);
+    const int64_t n = d.batch * d.dim_len * d.after;
+    if (n == 0) {
+        return OPSGNN_OK;
+    }
+    if (out == nullptr || src == nullptr || index == nullptr || perm == nullptr) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (workspace == nullptr || workspace_bytes < l.total_bytes || !Aligned(workspace, 256)) {
+        return OPSGNN_ERR_WORKSPACE;
+    }
+    Params p = MakeParams(d, static_cast<char*>(workspace), l);
+    p.src = src;
+    p.index = index;
+    p.out = out;
+    cudaStream_t s = AsStream(stream);
+    switch (d.dtype) {
+        case OPSGNN_F32:
+            return Forward<float>(d, p, static_cast<char*>(workspace), l, s, perm);
+        case OPSGNN_F16:
+            return Forward<__half>(d, p, static_cast<char*>(workspace), l, s, perm);
+        default:
+            return Forward<__nv_bfloat16>(d, p, static_cast<char*>(workspace), l, s, perm);
     }
 }
 

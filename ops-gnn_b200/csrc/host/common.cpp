@@ -1,49 +1,121 @@
 #include "common.h"
 
+#include <ATen/cuda/CUDAEvent.h>
+#include <ATen/record_function.h>
+#include <c10/cuda/CUDACachingAllocator.h>
 #include <c10/cuda/CUDAException.h>
 #include <c10/util/intrusive_ptr.h>
 #include <cuda_runtime_api.h>
 
+#include <atomic>
 #include <list>
+#include <memory>
 #include <mutex>
 
 namespace opsgnn {
+
+// ---- write clock ---------------------------------------------------------------------------------------------------------
 namespace {
 
-// Identity of a tensor's contents as far as torch can see them: the implementation object, its version counter and
-// the storage address.  Inference tensors have no version counter and are never cached.
-struct TensorKey {
-    const c10::TensorImpl* impl = nullptr;
-    const void* data = nullptr;
-    int64_t version = -1;
-    int64_t numel = 0;
-    std::optional<c10::weak_intrusive_ptr<c10::TensorImpl>> alive;
+std::atomic<uint64_t> g_write_clock{1};
+std::atomic<int64_t> g_foreign_in_flight{0};
+std::atomic<bool> g_observing{false};
+thread_local int t_planner_depth = 0;
+thread_local bool t_observable = true;
 
-    static std::optional<TensorKey> Of(const at::Tensor& t)
-    {
-        if (!t.defined() || t.is_inference()) {
-            return std::nullopt;
-        }
-        TensorKey key;
-        key.impl = t.unsafeGetTensorImpl();
-        key.data = t.const_data_ptr();
-        key.version = t._version();
-        key.numel = t.numel();
-        key.alive = c10::weak_intrusive_ptr<c10::TensorImpl>(t.getIntrusivePtr());
-        return key;
-    }
+struct ForeignOperator : at::ObserverContext {};
 
-    bool Matches(const TensorKey& other) const
-    {
-        return impl == other.impl && data == other.data && version == other.version && numel == other.numel &&
-               alive.has_value() && !alive->expired();
+std::unique_ptr<at::ObserverContext> OnOperatorStart(const at::RecordFunction&)
+{
+    if (t_planner_depth != 0) {
+        return nullptr;  // the planner's own ATen work
     }
-};
+    g_foreign_in_flight.fetch_add(1, std::memory_order_acq_rel);
+    g_write_clock.fetch_add(1, std::memory_order_acq_rel);
+    return std::make_unique<ForeignOperator>();
+}
+
+void OnOperatorEnd(const at::RecordFunction&, at::ObserverContext* context)
+{
+    if (context == nullptr) {
+        return;
+    }
+    g_write_clock.fetch_add(1, std::memory_order_acq_rel);
+    g_foreign_in_flight.fetch_sub(1, std::memory_order_acq_rel);
+}
+
+}  // namespace
+
+void StartWriteObserver()
+{
+    // Once, at module import (global callbacks must not be added while operators run in parallel); kept for the life of
+    // the process.
+    static const auto handle = at::addGlobalCallback(at::RecordFunctionCallback(OnOperatorStart, OnOperatorEnd)
+                                                         .needsInputs(false)
+                                                         .needsOutputs(false)
+                                                         .scopes({at::RecordScope::FUNCTION}));
+    (void)handle;
+    g_observing.store(true, std::memory_order_release);
+}
+
+uint64_t WriteClock() { return g_write_clock.load(std::memory_order_acquire); }
+
+bool WriteClockCurrent(uint64_t stamp)
+{
+    return t_observable && g_observing.load(std::memory_order_acquire) &&
+           g_foreign_in_flight.load(std::memory_order_acquire) == 0 && WriteClock() == stamp;
+}
+
+void NoteCallerMemoryWritten() { g_write_clock.fetch_add(1, std::memory_order_acq_rel); }
+
+PlannerScope::PlannerScope() : could_observe_(t_observable)
+{
+    // With operator recording switched off on this thread nothing can be observed: make every cached fact stale.
+    t_observable = could_observe_ && at::isRecordFunctionEnabled();
+    if (!t_observable) {
+        NoteCallerMemoryWritten();
+    }
+    ++t_planner_depth;
+}
+
+PlannerScope::~PlannerScope()
+{
+    --t_planner_depth;
+    t_observable = could_observe_;
+}
+
+std::optional<TensorKey> TensorKey::Of(const at::Tensor& t)
+{
+    if (!t.defined() || t.is_inference()) {
+        return std::nullopt;
+    }
+    TensorKey key;
+    key.impl = t.unsafeGetTensorImpl();
+    key.data = t.const_data_ptr();
+    key.version = t._version();
+    key.offset = t.storage_offset();
+    key.clock = WriteClock();
+    key.sizes = t.sizes().vec();
+    key.strides = t.strides().vec();
+    key.alive = c10::weak_intrusive_ptr<c10::TensorImpl>(t.getIntrusivePtr());
+    return key;
+}
+
+bool TensorKey::Matches(const TensorKey& now) const
+{
+    return impl == now.impl && data == now.data && version == now.version && offset == now.offset &&
+           sizes == now.sizes && strides == now.strides && alive.has_value() && !alive->expired() &&
+           WriteClockCurrent(clock);
+}
+
+namespace {
 
 struct PlanEntry {
     TensorKey ptr;
     int64_t rows, nnz;
     at::Tensor plan;
+    std::shared_ptr<at::cuda::CUDAEvent> built;  // recorded after PlanKernel on the stream that built the plan
+    cudaStream_t stream;
 };
 
 struct FactsEntry {
@@ -63,12 +135,20 @@ std::list<FactsEntry> g_facts;
 at::Tensor CsrPlan(const at::Tensor& ptr, int64_t rows, int64_t nnz_bound)
 {
     auto key = TensorKey::Of(ptr);
+    const auto current = c10::cuda::getCurrentCUDAStream(ptr.device().index());
     if (key) {
         std::lock_guard<std::mutex> lock(g_mutex);
         for (auto it = g_plans.begin(); it != g_plans.end(); ++it) {
             if (it->rows == rows && it->nnz == nnz_bound && it->ptr.Matches(*key)) {
                 g_plans.splice(g_plans.begin(), g_plans, it);
-                return g_plans.front().plan;
+                PlanEntry& hit = g_plans.front();
+                if (hit.stream != current.stream()) {
+                    // another stream built it: wait for its kernel, and keep the allocator from recycling the plan
+                    // under this stream should the entry be evicted while this stream still reads it
+                    hit.built->block(current);
+                    c10::cuda::CUDACachingAllocator::recordStream(hit.plan.storage().data_ptr(), current);
+                }
+                return hit.plan;
             }
         }
     }
@@ -79,8 +159,10 @@ at::Tensor CsrPlan(const at::Tensor& ptr, int64_t rows, int64_t nnz_bound)
                                       plan.data_ptr(), CurrentStream(ptr)),
                 "csr_plan");
     if (key) {
+        auto built = std::make_shared<at::cuda::CUDAEvent>();
+        built->record(current);
         std::lock_guard<std::mutex> lock(g_mutex);
-        g_plans.push_front(PlanEntry{*key, rows, nnz_bound, plan});
+        g_plans.push_front(PlanEntry{*key, rows, nnz_bound, plan, built, current.stream()});
         if (g_plans.size() > kCacheEntries) {
             g_plans.pop_back();
         }
@@ -133,6 +215,12 @@ void ClearCsrFactsCache()
 {
     std::lock_guard<std::mutex> lock(g_mutex);
     g_facts.clear();
+}
+
+std::tuple<int64_t, int64_t, int64_t> NativeCacheSizes()
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    return {static_cast<int64_t>(g_plans.size()), static_cast<int64_t>(g_facts.size()), SortedIndexCacheSize()};
 }
 
 namespace {

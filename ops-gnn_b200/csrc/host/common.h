@@ -75,8 +75,74 @@ inline int64_t Product(c10::IntArrayRef sizes, int64_t from, int64_t to)
     return p;
 }
 
-// Merge-path plan of a pointer array, cached per tensor identity and version (a GNN calls the same graph every layer
-// and every step).  Entries hold a weak reference, so a recycled address cannot revive a stale plan.
+// ---- when may a fact derived from a tensor's contents be reused? ---------------------------------------------------------
+// The planners cache facts that depend on what an index tensor HOLDS (the merge-path plan of a pointer array, the
+// validity mask of a CSR pair, whether a label vector is sorted).  A tensor's version counter sees in-place ATen
+// writes, but not a write through `tensor.data`, through an independent `set_()` alias of the same storage, or by a
+// kernel of this library into a caller-supplied `out=` that aliases an older input.  The reference closes that gap
+// (csrc/npu/common/spmm/host_proof_cache.h:36-83, 150-200) by treating ANY ATen operation that runs between two of its
+// calls as a possible write, and so does this build: a process-wide write clock advances whenever an ATen operator
+// starts or ends outside a planner (a global RecordFunction callback, installed at module import) and whenever a
+// planner is handed caller memory to write.  A cached fact carries the clock value it was made under and is reused
+// only while the clock has not moved, no foreign operator is in flight on another thread, and the tensor's identity,
+// version, address and layout are unchanged.  Back-to-back calls on one graph (a timing loop, the layers of a model
+// that only calls this library) hit the caches; anything else re-derives the fact with one small kernel.
+// Writes no host code can see (a raw-pointer write from another library, a peer GPU's store) remain the caller's
+// business: call clear_native_caches() after them.
+void StartWriteObserver();
+uint64_t WriteClock();
+bool WriteClockCurrent(uint64_t stamp);
+void NoteCallerMemoryWritten();
+// A planner about to write a caller-supplied `out`.  Every cached fact describes an INTEGER tensor (pointers, columns,
+// labels), so only an integer `out` can overwrite one; floating outputs leave the clock alone (reinterpreting a float
+// buffer as an index tensor of a later call is outside the contract).
+inline void NoteCallerOutput(const at::Tensor& out)
+{
+    if (out.defined() && !out.is_floating_point()) {
+        NoteCallerMemoryWritten();
+    }
+}
+
+// RAII around one planner call: ATen work the planner does itself (allocations, contiguous copies, the 4-byte read of
+// a validation mask) is not a foreign write.
+class PlannerScope {
+public:
+    PlannerScope();
+    ~PlannerScope();
+    PlannerScope(const PlannerScope&) = delete;
+    PlannerScope& operator=(const PlannerScope&) = delete;
+
+private:
+    bool could_observe_;
+};
+
+// Wraps a planner for binding: the whole call runs inside a PlannerScope.
+template <class R, class... A> auto Scoped(R (*fn)(A...))
+{
+    return [fn](A... args) -> R {
+        PlannerScope scope;
+        return fn(std::forward<A>(args)...);
+    };
+}
+
+// Identity of a tensor's contents as far as the host can see them (see above).  Inference tensors have no version
+// counter and are never cached.
+struct TensorKey {
+    const c10::TensorImpl* impl = nullptr;
+    const void* data = nullptr;
+    int64_t version = -1;
+    int64_t offset = 0;
+    uint64_t clock = 0;
+    std::vector<int64_t> sizes, strides;
+    std::optional<c10::weak_intrusive_ptr<c10::TensorImpl>> alive;
+
+    static std::optional<TensorKey> Of(const at::Tensor& t);
+    bool Matches(const TensorKey& now) const;   // `now` = TensorKey::Of(the tensor presented by the current call)
+};
+
+// Merge-path plan of a pointer array, cached per tensor identity, version and write clock (a GNN calls the same graph
+// every layer and every step).  Entries hold a weak reference, so a recycled address cannot revive a stale plan.  A plan
+// built on one stream and reused on another is ordered by an event recorded after its kernel.
 at::Tensor CsrPlan(const at::Tensor& ptr, int64_t rows, int64_t nnz_bound);
 void ClearCsrPlanCache();
 
@@ -107,5 +173,8 @@ int64_t DeviceStallCount(int device, bool synchronize);
 // device-to-host read on a miss.
 int CsrFacts(const at::Tensor& ptr, const std::optional<at::Tensor>& col, int64_t rows, int64_t cols, int64_t nnz);
 void ClearCsrFactsCache();
+void ClearSortedIndexCache();                          // grouped.cpp: the sortedness facts of label vectors
+int64_t SortedIndexCacheSize();
+std::tuple<int64_t, int64_t, int64_t> NativeCacheSizes();  // plans, validation facts, sortedness facts
 
 }  // namespace opsgnn

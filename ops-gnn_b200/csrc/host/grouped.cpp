@@ -14,45 +14,67 @@
 namespace opsgnn {
 namespace {
 
+// What the planner knows about a label vector, derived once per (tensor, version, write clock): is it sorted, how long
+// is its longest group, and - for an unsorted vector with short groups only - the stable permutation that sorts it.
+struct IndexFacts {
+    bool sorted = false;
+    int64_t longest = 0;   // rows of the largest group
+    at::Tensor perm;       // int64 stable argsort, defined only when !sorted and longest <= OPSGNN_GROUPED_SHORT_GROUP
+    bool measured = false; // longest (and perm) were derived; false for an unsorted vector nobody asked to sort yet
+};
 struct SortedEntry {
-    const c10::TensorImpl* impl;
-    const void* data;
-    int64_t version, numel;
-    std::optional<c10::weak_intrusive_ptr<c10::TensorImpl>> alive;
-    bool sorted;
+    TensorKey index;
+    IndexFacts facts;
 };
 std::mutex g_sorted_mutex;
 std::list<SortedEntry> g_sorted;
 
-// True when the index is non-decreasing.  One kernel and an 8-byte read on a miss; nothing on a hit.
-bool IndexIsSorted(const at::Tensor& index)
+// One statistics kernel and a 24-byte read on a miss, plus - to learn the longest group - a run-length pass over the
+// (sorted) labels; an unsorted vector is argsorted once and the permutation kept.  Nothing on a hit.  The facts are
+// reused under the rules of TensorKey (identity, version, layout and the write clock): a stale "sorted" would send an
+// unsorted index down the sorted path.
+IndexFacts FactsOf(const at::Tensor& index, bool want_permutation)
 {
-    const bool cacheable = !index.is_inference();
-    const c10::TensorImpl* impl = index.unsafeGetTensorImpl();
-    const int64_t version = cacheable ? static_cast<int64_t>(index._version()) : -1;
-    if (cacheable) {
+    auto key = TensorKey::Of(index);
+    if (key) {
         std::lock_guard<std::mutex> lock(g_sorted_mutex);
         for (auto it = g_sorted.begin(); it != g_sorted.end(); ++it) {
-            if (it->impl == impl && it->data == index.const_data_ptr() && it->version == version &&
-                it->numel == index.numel() && it->alive && !it->alive->expired()) {
-                return it->sorted;
+            if (it->index.Matches(*key) && (it->facts.measured || !want_permutation)) {
+                return it->facts;
             }
         }
     }
+    IndexFacts facts;
     auto stats = at::empty({3}, index.options().dtype(at::kLong));
     CheckStatus(opsgnn_index_stats(index.const_data_ptr(), DtypeId(index.scalar_type(), "grouped"), index.numel(),
                                    stats.data_ptr<int64_t>(), CurrentStream(index)),
                 "grouped");
-    const bool sorted = stats[2].item<int64_t>() == 1;
-    if (cacheable) {
+    facts.sorted = stats[2].item<int64_t>() == 1;
+    at::Tensor ordered = index;
+    at::Tensor perm;
+    if (!facts.sorted && want_permutation) {
+        perm = at::argsort(index, /*stable=*/true, /*dim=*/0, /*descending=*/false);
+        ordered = index.index_select(0, perm);
+    }
+    if (facts.sorted || want_permutation) {
+        auto runs = at::unique_consecutive(ordered, /*return_inverse=*/false, /*return_counts=*/true);
+        facts.longest = std::get<2>(runs).numel() > 0 ? std::get<2>(runs).max().item<int64_t>() : 0;
+        if (!facts.sorted && facts.longest <= OPSGNN_GROUPED_SHORT_GROUP) {
+            facts.perm = perm;
+        }
+        facts.measured = true;
+    } else {
+        facts.longest = index.numel();  // unknown: treat as long
+    }
+    if (key) {
         std::lock_guard<std::mutex> lock(g_sorted_mutex);
-        g_sorted.push_front(SortedEntry{impl, index.const_data_ptr(), version, index.numel(),
-                                        c10::weak_intrusive_ptr<c10::TensorImpl>(index.getIntrusivePtr()), sorted});
+        g_sorted.remove_if([&](const SortedEntry& entry) { return entry.index.impl == key->impl; });
+        g_sorted.push_front(SortedEntry{*key, facts});
         if (g_sorted.size() > 32) {
             g_sorted.pop_back();
         }
     }
-    return sorted;
+    return facts;
 }
 
 struct View {
@@ -101,11 +123,30 @@ at::Tensor Forward(const at::Tensor& src, const at::Tensor& index, int64_t dim, 
     if (out.numel() == 0) {
         return out;
     }
-    const bool sorted = index.numel() > 0 && IndexIsSorted(index);
-    OpsgnnGroupedDesc desc = MakeDesc(v, src, index, dim_size, mode, sorted);
+    // The single-read kernel takes one batch of rows made of whole 16-byte vectors; softmax and log-softmax only.
+    const int64_t vec = 16 / static_cast<int64_t>(src.element_size());
+    const bool short_shape = mode != OPSGNN_GROUPED_LOGSUMEXP && v.batch == 1 && v.after % vec == 0 &&
+                             reinterpret_cast<uintptr_t>(src.const_data_ptr()) % 16 == 0 &&
+                             reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0;
+    IndexFacts facts;
+    if (index.numel() > 0) {
+        facts = FactsOf(index, short_shape);
+    }
+    const bool short_groups = short_shape && facts.longest <= OPSGNN_GROUPED_SHORT_GROUP;
+    OpsgnnGroupedDesc desc = MakeDesc(v, src, index, dim_size, mode, facts.sorted);
+    if (short_groups && (facts.sorted || facts.perm.defined())) {
+        desc.sorted = OPSGNN_GROUPED_SORTED_SHORT;
+    }
     int64_t bytes = 0;
     CheckStatus(opsgnn_grouped_workspace_bytes(&desc, &bytes), api);
     at::Tensor scratch = Scratch(bytes, out);
+    if (short_groups && !facts.sorted && facts.perm.defined()) {
+        CheckStatus(opsgnn_grouped_forward_permuted(&desc, src.const_data_ptr(), index.const_data_ptr(),
+                                                    facts.perm.const_data_ptr<int64_t>(), out.data_ptr(), scratch.data_ptr(),
+                                                    scratch.numel(), CurrentStream(out)),
+                    api);
+        return out;
+    }
     CheckStatus(opsgnn_grouped_forward(&desc, src.const_data_ptr(), index.const_data_ptr(), out.data_ptr(),
                                        scratch.data_ptr(), scratch.numel(), CurrentStream(out)),
                 api);
@@ -178,6 +219,18 @@ at::Tensor scatter_logsumexp_backward(const at::Tensor& src, const at::Tensor& o
     return Backward(&src, out, grad_out, index, dim, dim_size, OPSGNN_GROUPED_LOGSUMEXP, "scatter_logsumexp");
 }
 
+void ClearSortedIndexCache()
+{
+    std::lock_guard<std::mutex> lock(g_sorted_mutex);
+    g_sorted.clear();
+}
+
+int64_t SortedIndexCacheSize()
+{
+    std::lock_guard<std::mutex> lock(g_sorted_mutex);
+    return static_cast<int64_t>(g_sorted.size());
+}
+
 }  // namespace opsgnn
 
 namespace py = pybind11;
@@ -185,19 +238,19 @@ namespace py = pybind11;
 void BindGrouped(py::module_& m)
 {
     using namespace opsgnn;
-    m.def("scatter_softmax_forward", &scatter_softmax_forward, py::arg("src"), py::arg("index"), py::arg("dim"),
+    m.def("scatter_softmax_forward", opsgnn::Scoped(&scatter_softmax_forward), py::arg("src"), py::arg("index"), py::arg("dim"),
           py::arg("dim_size"), "Grouped softmax forward on CUDA", py::call_guard<py::gil_scoped_release>());
-    m.def("scatter_softmax_backward", &scatter_softmax_backward, py::arg("out"), py::arg("grad_out"), py::arg("index"),
+    m.def("scatter_softmax_backward", opsgnn::Scoped(&scatter_softmax_backward), py::arg("out"), py::arg("grad_out"), py::arg("index"),
           py::arg("dim"), py::arg("dim_size"), "Grouped softmax backward on CUDA",
           py::call_guard<py::gil_scoped_release>());
-    m.def("scatter_log_softmax_forward", &scatter_log_softmax_forward, py::arg("src"), py::arg("index"), py::arg("dim"),
+    m.def("scatter_log_softmax_forward", opsgnn::Scoped(&scatter_log_softmax_forward), py::arg("src"), py::arg("index"), py::arg("dim"),
           py::arg("dim_size"), "Grouped log-softmax forward on CUDA", py::call_guard<py::gil_scoped_release>());
-    m.def("scatter_log_softmax_backward", &scatter_log_softmax_backward, py::arg("out"), py::arg("grad_out"),
+    m.def("scatter_log_softmax_backward", opsgnn::Scoped(&scatter_log_softmax_backward), py::arg("out"), py::arg("grad_out"),
           py::arg("index"), py::arg("dim"), py::arg("dim_size"), "Grouped log-softmax backward on CUDA",
           py::call_guard<py::gil_scoped_release>());
-    m.def("scatter_logsumexp_forward", &scatter_logsumexp_forward, py::arg("src"), py::arg("index"), py::arg("dim"),
+    m.def("scatter_logsumexp_forward", opsgnn::Scoped(&scatter_logsumexp_forward), py::arg("src"), py::arg("index"), py::arg("dim"),
           py::arg("dim_size"), "Grouped log-sum-exp forward on CUDA", py::call_guard<py::gil_scoped_release>());
-    m.def("scatter_logsumexp_backward", &scatter_logsumexp_backward, py::arg("src"), py::arg("out"), py::arg("grad_out"),
+    m.def("scatter_logsumexp_backward", opsgnn::Scoped(&scatter_logsumexp_backward), py::arg("src"), py::arg("out"), py::arg("grad_out"),
           py::arg("index"), py::arg("dim"), py::arg("dim_size"), "Grouped log-sum-exp backward on CUDA",
           py::call_guard<py::gil_scoped_release>());
 }

@@ -47,6 +47,15 @@ at::Tensor ptr2ind(at::Tensor ptr, int64_t E);
 at::Tensor index_stats(at::Tensor index);
 int64_t csr_facts(at::Tensor ptr, std::optional<at::Tensor> col, int64_t rows, int64_t cols, int64_t nnz);
 
+// fused graph attention (attention.cpp)
+std::tuple<at::Tensor, at::Tensor> GatAggregate(const at::Tensor& indptr, const at::Tensor& indices, const at::Tensor& edge_rows,
+                                                const at::Tensor& x, const at::Tensor& left, const at::Tensor& right,
+                                                double negative_slope);
+
+// row expansions (gather.cpp)
+at::Tensor gather_csr(const at::Tensor& src, const at::Tensor& indptr, const std::optional<at::Tensor>& out);
+at::Tensor gather_coo(const at::Tensor& src, const at::Tensor& index, const std::optional<at::Tensor>& out);
+
 // SDDMM (sddmm.cpp)
 at::Tensor SddmmCsrForward(const at::Tensor& indptr, const at::Tensor& indices, const std::optional<at::Tensor>& lhs,
                            const std::optional<at::Tensor>& rhs, const std::string& op, int64_t lhs_target,

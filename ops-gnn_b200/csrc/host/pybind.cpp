@@ -22,52 +22,53 @@ bool HasKernelForKey(const std::string& op_name, c10::DispatchKey key)
 void BindSpmm(py::module_& m)
 {
     using namespace opsgnn;
-    m.def("spmm_max_csr", &SpmmMaxCsr, py::arg("indptr"), py::arg("indices"), py::arg("x"), py::arg("out") = py::none(),
+    m.def("spmm_max_csr", opsgnn::Scoped(&SpmmMaxCsr), py::arg("indptr"), py::arg("indices"), py::arg("x"), py::arg("out") = py::none(),
           "CSR SpMM max on CUDA", py::call_guard<py::gil_scoped_release>());
-    m.def("spmm_min_csr", &SpmmMinCsr, py::arg("indptr"), py::arg("indices"), py::arg("x"), py::arg("out") = py::none(),
+    m.def("spmm_min_csr", opsgnn::Scoped(&SpmmMinCsr), py::arg("indptr"), py::arg("indices"), py::arg("x"), py::arg("out") = py::none(),
           "CSR SpMM min on CUDA", py::call_guard<py::gil_scoped_release>());
-    m.def("spmm_sum_csr", &SpmmSumCsr, py::arg("indptr"), py::arg("indices"), py::arg("x"), py::arg("out") = py::none(),
+    m.def("spmm_sum_csr", opsgnn::Scoped(&SpmmSumCsr), py::arg("indptr"), py::arg("indices"), py::arg("x"), py::arg("out") = py::none(),
           "CSR SpMM sum on CUDA", py::call_guard<py::gil_scoped_release>());
-    m.def("unified_spmm_csr", &UnifiedSpmmCsr, py::arg("indptr"), py::arg("indices"), py::arg("x"),
+    m.def("unified_spmm_csr", opsgnn::Scoped(&UnifiedSpmmCsr), py::arg("indptr"), py::arg("indices"), py::arg("x"),
           py::arg("op") = "copy_lhs", py::arg("reduce") = "sum", py::arg("out") = py::none(),
           "Unified two-dimensional CSR SpMM on CUDA", py::call_guard<py::gil_scoped_release>());
-    m.def("spmm_weighted_csr", &SpmmWeightedCsr, py::arg("indptr"), py::arg("indices"), py::arg("x"), py::arg("weight"),
+    m.def("spmm_weighted_csr", opsgnn::Scoped(&SpmmWeightedCsr), py::arg("indptr"), py::arg("indices"), py::arg("x"), py::arg("weight"),
           py::arg("reduce") = "sum",
           "CSR SpMM with one edge weight per feature group (fused `mul` message); not part of the reference binding",
           py::call_guard<py::gil_scoped_release>());
-    m.def("gather_rows", &GatherRows, py::arg("x"), py::arg("index"), py::arg("unit_ptr"), py::arg("out"),
+    m.def("gather_rows", opsgnn::Scoped(&GatherRows), py::arg("x"), py::arg("index"), py::arg("unit_ptr"), py::arg("out"),
           "out[i] = x[index[i]] through the CSR engine (unit_ptr = 0..n); not part of the reference binding",
           py::call_guard<py::gil_scoped_release>());
-    m.def("gather_rows_into", &GatherRowsInto, py::arg("x"), py::arg("index"), py::arg("outs"), py::arg("max_ctas") = 0,
+    m.def("gather_rows_into", opsgnn::Scoped(&GatherRowsInto), py::arg("x"), py::arg("index"), py::arg("outs"), py::arg("max_ctas") = 0,
           "outs[s][i] = x[index[start_s + i]] with a capped grid; the outputs may be views of a peer's mapped buffer; not "
           "part of the reference binding",
           py::call_guard<py::gil_scoped_release>());
-    m.def("csr_spmm_into", &CsrSpmmInto, py::arg("ptr"), py::arg("col"), py::arg("value"), py::arg("x"), py::arg("out"),
+    m.def("csr_spmm_into", opsgnn::Scoped(&CsrSpmmInto), py::arg("ptr"), py::arg("col"), py::arg("value"), py::arg("x"), py::arg("out"),
           "out[r] = sum_e value[e] * x[col[e]] into a caller-provided contiguous [rows, K] view; not part of the reference "
           "binding",
           py::call_guard<py::gil_scoped_release>());
     auto sub = m.def_submodule("torch_sparse_spmm", "torch_sparse SpMM on CUDA");
-    sub.def("forward", &TorchSparseSpmmForward, py::arg("ptr"), py::arg("col"), py::arg("value"), py::arg("mat"),
+    sub.def("forward", opsgnn::Scoped(&TorchSparseSpmmForward), py::arg("ptr"), py::arg("col"), py::arg("value"), py::arg("mat"),
             py::arg("reduce"), py::arg("outtype"), py::call_guard<py::gil_scoped_release>());
-    sub.def("validate", &TorchSparseSpmmValidate, py::arg("ptr"), py::arg("col"), py::arg("n"),
+    sub.def("validate", opsgnn::Scoped(&TorchSparseSpmmValidate), py::arg("ptr"), py::arg("col"), py::arg("n"),
             py::call_guard<py::gil_scoped_release>());
-    sub.def("value_backward", &TorchSparseSpmmValueGrad, py::arg("ptr"), py::arg("col"), py::arg("mat"), py::arg("grad"),
+    sub.def("value_backward", opsgnn::Scoped(&TorchSparseSpmmValueGrad), py::arg("ptr"), py::arg("col"), py::arg("mat"), py::arg("grad"),
             py::arg("reduce"), py::arg("width"), py::call_guard<py::gil_scoped_release>());
-    sub.def("convert", &TorchSparseSpmmConvert, py::arg("src"), py::arg("output"), py::arg("to_ptr"),
+    sub.def("convert", opsgnn::Scoped(&TorchSparseSpmmConvert), py::arg("src"), py::arg("output"), py::arg("to_ptr"),
             py::call_guard<py::gil_scoped_release>());
-    sub.def("permute_values", &TorchSparseSpmmPermuteValues, py::arg("value"), py::arg("perm"),
+    sub.def("permute_values", opsgnn::Scoped(&TorchSparseSpmmPermuteValues), py::arg("value"), py::arg("perm"),
             py::call_guard<py::gil_scoped_release>());
-    sub.def("tensor_version", &TorchSparseSpmmTensorVersion, py::arg("tensor"));
+    sub.def("tensor_version", opsgnn::Scoped(&TorchSparseSpmmTensorVersion), py::arg("tensor"));
 }
 
 void BindSegment(py::module_& m)
 {
     using namespace opsgnn;
-    m.def("segment_csr", &segment_csr, py::arg("src"), py::arg("indptr"), py::arg("out") = py::none(),
+    m.def("segment_csr", opsgnn::Scoped(&segment_csr), py::arg("src"), py::arg("indptr"), py::arg("out") = py::none(),
           py::arg("reduce") = "sum", py::arg("return_arg") = true, py::call_guard<py::gil_scoped_release>());
     m.def(
         "segment_csr_value",
         [](at::Tensor src, at::Tensor indptr, std::optional<at::Tensor> out, const std::string& reduce) {
+            PlannerScope scope;
             return segment_csr(std::move(src), std::move(indptr), std::move(out), reduce, false)[0];
         },
         py::arg("src"), py::arg("indptr"), py::arg("out") = py::none(), py::arg("reduce") = "sum",
@@ -76,35 +77,36 @@ void BindSegment(py::module_& m)
     m.attr("SEGMENT_COO_MEAN") = static_cast<int32_t>(SEGMENT_COO_MEAN);
     m.attr("SEGMENT_COO_MIN") = static_cast<int32_t>(SEGMENT_COO_MIN);
     m.attr("SEGMENT_COO_MAX") = static_cast<int32_t>(SEGMENT_COO_MAX);
-    m.def("segment_coo_forward", &segment_coo_forward, py::arg("src"), py::arg("index"), py::arg("out"),
+    m.def("segment_coo_forward", opsgnn::Scoped(&segment_coo_forward), py::arg("src"), py::arg("index"), py::arg("out"),
           py::arg("dim_size"), py::arg("reduce"), py::arg("return_arg") = true,
           py::call_guard<py::gil_scoped_release>());
     m.def(
         "segment_coo_value",
         [](at::Tensor src, at::Tensor index, std::optional<at::Tensor> out, std::optional<int64_t> dim_size,
            int64_t reduce) {
+            PlannerScope scope;
             return std::get<0>(segment_coo_forward(std::move(src), std::move(index), std::move(out), dim_size, reduce,
                                                    false));
         },
         py::arg("src"), py::arg("index"), py::arg("out"), py::arg("dim_size"), py::arg("reduce"),
         py::call_guard<py::gil_scoped_release>());
-    m.def("segment_logsumexp_forward", &segment_logsumexp_forward, py::arg("src"), py::arg("indptr"),
+    m.def("segment_logsumexp_forward", opsgnn::Scoped(&segment_logsumexp_forward), py::arg("src"), py::arg("indptr"),
           "CSR log-sum-exp forward on CUDA", py::call_guard<py::gil_scoped_release>());
 }
 
 void BindConvert(py::module_& m)
 {
     using namespace opsgnn;
-    m.def("ind2ptr", &ind2ptr, py::arg("ind"), py::arg("M"),
+    m.def("ind2ptr", opsgnn::Scoped(&ind2ptr), py::arg("ind"), py::arg("M"),
           "Convert sorted row indices to CSR row pointer, same as torch_sparse.ind2ptr",
           py::call_guard<py::gil_scoped_release>());
-    m.def("ptr2ind", &ptr2ind, py::arg("ptr"), py::arg("E"),
+    m.def("ptr2ind", opsgnn::Scoped(&ptr2ind), py::arg("ptr"), py::arg("E"),
           "Convert CSR row pointer to row indices, same as torch_sparse.ptr2ind",
           py::call_guard<py::gil_scoped_release>());
-    m.def("csr_facts", &csr_facts, py::arg("ptr"), py::arg("col"), py::arg("rows"), py::arg("cols"), py::arg("nnz"),
+    m.def("csr_facts", opsgnn::Scoped(&csr_facts), py::arg("ptr"), py::arg("col"), py::arg("rows"), py::arg("cols"), py::arg("nnz"),
           "Validation bit mask of a CSR structure: 1 end points, 2 pointer range, 4 decreasing pointer, 8 column range",
           py::call_guard<py::gil_scoped_release>());
-    m.def("index_stats", &index_stats, py::arg("index"),
+    m.def("index_stats", opsgnn::Scoped(&index_stats), py::arg("index"),
           "int64[3] on the device: minimum, maximum and 1 when the index is non-decreasing",
           py::call_guard<py::gil_scoped_release>());
 }
@@ -114,6 +116,8 @@ void BindConvert(py::module_& m)
 void BindSddmm(py::module_& m);
 void BindScatter(py::module_& m);
 void BindGrouped(py::module_& m);
+void BindGather(py::module_& m);
+void BindAttention(py::module_& m);
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
 {
@@ -125,10 +129,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
         py::arg("op_name"),
         "True if the operator already has a kernel for this build's device key (CUDA), e.g. a pre-existing "
         "third-party registration");
+    opsgnn::StartWriteObserver();
     m.def("clear_native_caches", []() {
         opsgnn::ClearCsrPlanCache();
         opsgnn::ClearCsrFactsCache();
+        opsgnn::ClearSortedIndexCache();
     });
+    m.def("write_clock", []() { return opsgnn::WriteClock(); },
+          "Value of the process-wide write clock: it advances whenever an ATen operator runs outside this library's "
+          "planners or a planner writes caller memory; cached plans and validation facts are reused only while it stands");
+    m.def("native_cache_sizes", []() { return opsgnn::NativeCacheSizes(); },
+          "(plans, validation facts, sorted-index facts) currently cached");
     m.def(
         "device_stall_count",
         [](int64_t device, bool synchronize) { return opsgnn::DeviceStallCount(static_cast<int>(device), synchronize); },
@@ -147,4 +158,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     BindSddmm(m);
     BindScatter(m);
     BindGrouped(m);
+    BindGather(m);
+    BindAttention(m);
 }

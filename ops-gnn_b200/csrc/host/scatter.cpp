@@ -25,6 +25,9 @@ std::tuple<at::Tensor, at::Tensor> scatter_forward(at::Tensor src, at::Tensor in
     for (int64_t d = 0; d < src.dim(); ++d) {
         TORCH_CHECK(d == dim || out.size(d) == src.size(d), "scatter: out shape must match src outside the scatter dim");
     }
+    if (has_out) {
+        NoteCallerOutput(out);
+    }
     const int64_t before = Product(src.sizes(), 0, dim);
     const int64_t dim_len = src.size(dim);
     const int64_t after = Product(src.sizes(), dim + 1, src.dim());
@@ -63,7 +66,7 @@ namespace py = pybind11;
 
 void BindScatter(py::module_& m)
 {
-    m.def("scatter_forward", &opsgnn::scatter_forward, py::arg("src"), py::arg("index"), py::arg("dim"), py::arg("out"),
+    m.def("scatter_forward", opsgnn::Scoped(&opsgnn::scatter_forward), py::arg("src"), py::arg("index"), py::arg("dim"), py::arg("out"),
           py::arg("reduce"), py::arg("has_out"), py::arg("hot_target") = -1,
           "torch_scatter-compatible forward reduction (CUDA)", py::call_guard<py::gil_scoped_release>());
 }

@@ -177,7 +177,7 @@ namespace py = pybind11;
 
 void BindSddmm(py::module_& m)
 {
-    m.def("sddmm_csr", &opsgnn::SddmmCsrForward, py::arg("indptr"), py::arg("indices"), py::arg("lhs"), py::arg("rhs"),
+    m.def("sddmm_csr", opsgnn::Scoped(&opsgnn::SddmmCsrForward), py::arg("indptr"), py::arg("indices"), py::arg("lhs"), py::arg("rhs"),
           py::arg("op") = "dot", py::arg("lhs_target") = 0, py::arg("rhs_target") = 2, py::arg("out") = py::none(),
           "CSR SDDMM on CUDA", py::call_guard<py::gil_scoped_release>());
 }

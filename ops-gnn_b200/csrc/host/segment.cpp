@@ -129,6 +129,7 @@ std::vector<at::Tensor> segment_csr(at::Tensor src, at::Tensor indptr, std::opti
     const bool has_out = outOpt.has_value() && outOpt->defined();
     at::Tensor out;
     if (has_out) {
+        NoteCallerOutput(*outOpt);
         TORCH_CHECK(outOpt->scalar_type() == src.scalar_type(), "out dtype (", outOpt->scalar_type(),
                     ") must match src (", src.scalar_type(), ")");
         TORCH_CHECK(outOpt->sizes() == c10::IntArrayRef(outShape), "out shape ", outOpt->sizes(), " must be ",
@@ -217,6 +218,7 @@ std::tuple<at::Tensor, at::Tensor> segment_coo_forward(at::Tensor src, at::Tenso
     const bool has_out = optional_out.has_value();
     if (has_out) {
         const auto& out = *optional_out;
+        NoteCallerOutput(out);
         TORCH_CHECK(out.device() == src.device() && out.scalar_type() == src.scalar_type(),
                     "out device and dtype must match src");
         TORCH_CHECK(out.dim() == src.dim(), "out rank mismatch");

@@ -289,6 +289,9 @@ at::Tensor RunCopyLhs(const at::Tensor& indptr, const at::Tensor& indices, const
                     ": out must not alias any input storage");
     }
     c10::cuda::CUDAGuard guard(x.device());
+    if (out) {
+        NoteCallerOutput(*out);
+    }
     auto ptr = indptr.contiguous();
     auto idx = indices.contiguous();
     CheckCsrFacts(ptr, idx, rows, sources, edges, api, true);
@@ -500,6 +503,9 @@ at::Tensor UnifiedSpmmCsr(const at::Tensor& indptr, const at::Tensor& indices, c
     }
     TORCH_CHECK(!copy_rhs || x.scalar_type() == at::kFloat, "unified_spmm_csr: copy_rhs supports only float32");
     c10::cuda::CUDAGuard guard(x.device());
+    if (out) {
+        NoteCallerOutput(*out);
+    }
     const int64_t k = x.size(0);
     const int64_t nnz = indices.numel();
     auto ptr = indptr.contiguous();

@@ -40,6 +40,9 @@ from .segment_coo import (
     segment_add_coo, segment_coo, segment_max_coo, segment_mean_coo, segment_min_coo, segment_sum_coo,
 )
 from .segment_logsumexp import segment_logsumexp
+from .gather_csr import gather_csr
+from .gather_coo import gather_coo
+from .gat_aggregate import gat_aggregate
 from .spmm import spmm
 from .sddmm_csr import sddmm_csr
 from .bspmm import bspmm
@@ -77,6 +80,7 @@ __all__ = [
     "segment_csr", "segment_sum_csr", "segment_add_csr", "segment_mean_csr", "segment_min_csr", "segment_max_csr",
     "segment_reduce",
     "segment_logsumexp",
+    "gather_csr", "gather_coo", "gat_aggregate",
     "segment_coo", "segment_sum_coo", "segment_add_coo", "segment_mean_coo", "segment_min_coo", "segment_max_coo",
     "scatter", "scatter_sum", "scatter_add", "scatter_mul", "scatter_mean", "scatter_min", "scatter_max",
     "native_available",

@@ -27,10 +27,11 @@ EXPORTS = (
     "opsgnn_csr_reduce_status", "opsgnn_set_status_sink", "opsgnn_set_wait_polls",
     "opsgnn_csr_integer_mean", "opsgnn_sddmm_workspace_bytes", "opsgnn_sddmm_csr", "opsgnn_sddmm_csr_static",
     "opsgnn_spmm_value_grad",
-    "opsgnn_gather_rows",
+    "opsgnn_attention_lse_workspace_bytes", "opsgnn_attention_lse", "opsgnn_attention_aggregate",
+    "opsgnn_gather_rows", "opsgnn_gather_expand",
     "opsgnn_ind2ptr", "opsgnn_ptr2ind", "opsgnn_csr_validate", "opsgnn_permute_values", "opsgnn_index_stats",
     "opsgnn_scatter_workspace_bytes", "opsgnn_scatter",
-    "opsgnn_grouped_workspace_bytes", "opsgnn_grouped_forward", "opsgnn_grouped_backward",
+    "opsgnn_grouped_workspace_bytes", "opsgnn_grouped_forward", "opsgnn_grouped_forward_permuted", "opsgnn_grouped_backward",
 )
 
 
@@ -48,6 +49,13 @@ class SddmmDesc(Structure):
         ("rows", c_int64), ("nnz", c_int64), ("feat", c_int64), ("lhs_rows", c_int64), ("rhs_rows", c_int64),
         ("op", c_int32), ("lhs_target", c_int32), ("rhs_target", c_int32), ("index_type", c_int32),
         ("dtype", c_int32),
+    ]
+
+
+class AttentionDesc(Structure):
+    _fields_ = [
+        ("rows", c_int64), ("src_rows", c_int64), ("heads", c_int64), ("width", c_int64), ("nnz", c_int64),
+        ("negative_slope", ctypes.c_float), ("index_type", c_int32), ("dtype", c_int32),
     ]
 
 
@@ -85,6 +93,12 @@ _PROTOTYPES = {
                                        c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "opsgnn_gather_rows": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, POINTER(c_int64),
                                    POINTER(c_void_p), c_int, c_void_p]),
+    "opsgnn_attention_lse_workspace_bytes": (c_int, [POINTER(AttentionDesc), POINTER(c_int64)]),
+    "opsgnn_attention_lse": (c_int, [POINTER(AttentionDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                     c_int64, c_void_p]),
+    "opsgnn_attention_aggregate": (c_int, [POINTER(AttentionDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "opsgnn_gather_expand": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "opsgnn_ind2ptr": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
     "opsgnn_ptr2ind": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
     "opsgnn_csr_validate": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
@@ -96,6 +110,8 @@ _PROTOTYPES = {
     "opsgnn_grouped_workspace_bytes": (c_int, [POINTER(GroupedDesc), POINTER(c_int64)]),
     "opsgnn_grouped_forward": (c_int, [POINTER(GroupedDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                        c_void_p]),
+    "opsgnn_grouped_forward_permuted": (c_int, [POINTER(GroupedDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                c_int64, c_void_p]),
     "opsgnn_grouped_backward": (c_int, [POINTER(GroupedDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_int64, c_void_p]),
 }

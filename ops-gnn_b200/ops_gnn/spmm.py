@@ -68,8 +68,10 @@ def _split_operands(request: _SpmmRequest) -> _Operands:
         node, edge = x, rhs
     tracked = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (node, edge))
     if not tracked:
-        node = node.detach() if node is not None else None
-        edge = edge.detach() if edge is not None else None
+        # Detach only what carries autograd state: a needless `detach()` is an ATen call, and any ATen call between two
+        # native calls makes the planners re-derive their cached CSR facts (they cannot tell it from a write).
+        node = node.detach() if node is not None and node.requires_grad else node
+        edge = edge.detach() if edge is not None and edge.requires_grad else edge
     return _Operands(node, edge, tracked)
 
 

@@ -376,6 +376,46 @@ def _remember_original(owner, name):
     return owner.__dict__.setdefault("_ops_gnn_originals", {}).setdefault(name, owner.__dict__[name])
 
 
+def register_dispatcher_kernels():
+    """Implement the six ``torch_sparse`` dispatcher operators of the SpMM path for CUDA tensors.
+
+    The reference registers ``spmm_sum``, ``spmm_mean``, ``spmm_min``, ``spmm_max``, ``ind2ptr`` and ``ptr2ind`` for its
+    device keys from Python (python/ops_gnn/torch_sparse_spmm.py:406-431); here the keys are ``CUDA`` and
+    ``AutogradCUDA``.  Only the operator SCHEMAS have to exist in the dispatcher (``torch_sparse`` defines them when it
+    is installed); an existing CUDA kernel of a CUDA build of ``torch_sparse`` is never shadowed.  Returns the names
+    that received a kernel, per key.  Called at import when ``torch_sparse`` is importable.
+    """
+    def op_sum(row, ptr, col, value, colptr, csr2csc, mat):
+        return _run(_Graph(ptr, col, row=row, colptr=colptr, csr2csc=csr2csc), value, mat, 0)[0]
+
+    def op_mean(row, ptr, col, value, rowcount, colptr, csr2csc, mat):
+        return _run(_Graph(ptr, col, row=row, rowcount=rowcount, colptr=colptr, csr2csc=csr2csc), value, mat, 1)[0]
+
+    table = {
+        "spmm_sum": op_sum,
+        "spmm_mean": op_mean,
+        "spmm_min": lambda ptr, col, value, mat: _run(_Graph(ptr, col), value, mat, 2),
+        "spmm_max": lambda ptr, col, value, mat: _run(_Graph(ptr, col), value, mat, 3),
+        "ind2ptr": lambda ind, rows: _native.convert(ind, rows + 1, True),
+        "ptr2ind": lambda ptr, edges: _native.convert(ptr, edges, False),
+    }
+    registered = {}
+    for key in ("CUDA", "AutogradCUDA"):
+        library = torch.library.Library("torch_sparse", "IMPL", key)
+        registered[key] = []
+        for name, implementation in table.items():
+            # A CUDA build of torch_sparse owns its own CUDA kernels; never shadow an existing registration.
+            if key == "CUDA" and _pybind.has_private_use1_kernel("torch_sparse::" + name):
+                continue
+            try:
+                library.impl(name, implementation)
+                registered[key].append(name)
+            except RuntimeError:
+                pass
+        _LIBRARIES.append(library)
+    return registered
+
+
 def _install_torch_sparse_hooks():  # pragma: no cover - needs the third-party package
     global _upstream_coo_spmm
     _upstream_coo_spmm = _remember_original(torch_sparse, "spmm")
@@ -421,31 +461,7 @@ def _install_torch_sparse_hooks():  # pragma: no cover - needs the third-party p
             return sparse_tensor_spmm(src, other, reduce)
         return upstream_matmul(src, other, reduce)
 
-    def op_sum(row, ptr, col, value, colptr, csr2csc, mat):
-        return _run(_Graph(ptr, col, row=row, colptr=colptr, csr2csc=csr2csc), value, mat, 0)[0]
-
-    def op_mean(row, ptr, col, value, rowcount, colptr, csr2csc, mat):
-        return _run(_Graph(ptr, col, row=row, rowcount=rowcount, colptr=colptr, csr2csc=csr2csc), value, mat, 1)[0]
-
-    table = {
-        "spmm_sum": op_sum,
-        "spmm_mean": op_mean,
-        "spmm_min": lambda ptr, col, value, mat: _run(_Graph(ptr, col), value, mat, 2),
-        "spmm_max": lambda ptr, col, value, mat: _run(_Graph(ptr, col), value, mat, 3),
-        "ind2ptr": lambda ind, rows: _native.convert(ind, rows + 1, True),
-        "ptr2ind": lambda ptr, edges: _native.convert(ptr, edges, False),
-    }
-    for key in ("CUDA", "AutogradCUDA"):
-        library = torch.library.Library("torch_sparse", "IMPL", key)
-        for name, implementation in table.items():
-            # A CUDA build of torch_sparse owns its own CUDA kernels; never shadow an existing registration.
-            if key == "CUDA" and _pybind.has_private_use1_kernel("torch_sparse::" + name):
-                continue
-            try:
-                library.impl(name, implementation)
-            except RuntimeError:
-                pass
-        _LIBRARIES.append(library)
+    register_dispatcher_kernels()
 
     torch_sparse.spmm = coo_spmm
     importlib.import_module("torch_sparse.spmm").spmm = coo_spmm

@@ -11,6 +11,7 @@ checks every oracle function against those fixtures and against the known-answer
 test files.
 """
 from .convert import ind2ptr_oracle, ptr2ind_oracle
+from .gather import gather_coo_oracle, gather_csr_oracle
 from .grouped import grouped_logsumexp_oracle, grouped_softmax_oracle
 from .scatter import scatter_oracle
 from .sddmm import sddmm_oracle
@@ -20,5 +21,5 @@ from .spmm import csr_spmm_oracle, spmm_copy_oracle
 __all__ = [
     "csr_spmm_oracle", "spmm_copy_oracle", "sddmm_oracle", "segment_csr_oracle", "segment_coo_oracle",
     "segment_logsumexp_oracle", "scatter_oracle", "grouped_softmax_oracle", "grouped_logsumexp_oracle",
-    "ind2ptr_oracle", "ptr2ind_oracle",
+    "ind2ptr_oracle", "ptr2ind_oracle", "gather_csr_oracle", "gather_coo_oracle",
 ]

@@ -287,6 +287,45 @@ def fixtures_convert():
     save("convert", cases)
 
 
+def fixtures_gather():
+    g = load("test/gather_csr/arch35/golden.py")
+    by_ptr, by_index = g["gather_csr_cpu"], g["gather_csr_coo_cpu"]
+    cases = []
+    # the golden file's own known-answer table, every dtype it lists
+    for src_data, index_data, ptr_data, expected in g["CASES"]:
+        for dtype in g["DTYPES"]:
+            src, ptr = torch.tensor(src_data, dtype=dtype), torch.tensor(ptr_data, dtype=torch.int64)
+            out = by_ptr(src, ptr)
+            assert torch.equal(out, torch.tensor(expected, dtype=dtype)) and torch.equal(by_index(src, ptr), out)
+            cases.append(dict(src=src, indptr=ptr, index=torch.tensor(index_data, dtype=torch.int64), out=out, source="table"))
+    # seeded cases: empty segments, an uncovered prefix, broadcast and per-batch pointers, wide and odd feature widths
+    gen = torch.Generator().manual_seed(91)
+    for shape, ptr_rank, prefix in (((40,), 1, 0), ((40, 7), 1, 3), ((3, 13, 16), 2, 0), ((3, 13, 5), 2, 2),
+                                    ((2, 3, 7, 9), 3, 0), ((9, 132), 1, 0), ((1, 9, 2, 3), 2, 1)):
+        for dtype in (torch.float32, torch.float16, torch.bfloat16, torch.float64, torch.int8, torch.uint8, torch.int16,
+                      torch.int32, torch.int64):
+            dim = ptr_rank - 1
+            segments = shape[dim]
+            lead = [1 if (ptr_rank == 1 or k % 2) else shape[k] for k in range(dim)] if ptr_rank > 1 else []
+            count = 1
+            for extent in lead:
+                count *= extent
+            rows = 37
+            cuts = torch.sort(torch.randint(prefix, rows + 1, (count, segments - 1), generator=gen), dim=1).values
+            ptr = torch.cat([torch.full((count, 1), prefix), cuts, torch.full((count, 1), rows)], dim=1).to(torch.int64)
+            ptr = ptr.reshape(lead + [segments + 1]) if lead else ptr.reshape(segments + 1)
+            src = (torch.randn(shape, generator=gen) * 9).to(dtype)
+            out = by_ptr(src, ptr)
+            case = dict(src=src, indptr=ptr, out=out, source="seeded")
+            if prefix == 0:
+                full = ptr.expand([shape[k] for k in range(dim)] + [segments + 1]).reshape(-1, segments + 1)
+                index = torch.stack([torch.arange(segments).repeat_interleave(row[1:] - row[:-1]) for row in full])
+                case["index"] = index.reshape([shape[k] for k in range(dim)] + [rows])
+                assert torch.equal(by_index(src, ptr), out)
+            cases.append(case)
+    save("gather", cases)
+
+
 if __name__ == "__main__":
     torch.set_num_threads(4)
     fixtures_torch_sparse_spmm()
@@ -298,3 +337,4 @@ if __name__ == "__main__":
     fixtures_grouped()
     fixtures_segment_logsumexp()
     fixtures_convert()
+    fixtures_gather()

@@ -42,6 +42,9 @@ def test_stalled_wait_is_reported_through_the_c_abi(cuda_device):
         assert b"wait" in lib.opsgnn_status_string(-5)
     finally:
         assert lib.opsgnn_set_wait_polls(-1) == 0
+        import ops_gnn
+
+        ops_gnn._pybind.device_stall_count(cuda_device.index or 0, True)   # the planner's sink saw the stall too: clear it
     got, _, workspace = _cabi.csr_reduce(*dev, _cabi.REDUCE_SUM, return_workspace=True)
     assert _cabi.csr_reduce_status(workspace) == 0
     want, _ = oracle.csr_spmm_oracle(*host, "sum", torch.float64)
@@ -53,7 +56,7 @@ def test_stalled_wait_raises_in_python(cuda_device):
     from ops_gnn.torch_sparse_spmm import csr_spmm
 
     host, dev = _inputs(cuda_device)
-    ops_gnn.check_device_status()                             # clean before the experiment
+    ops_gnn._pybind.device_stall_count(cuda_device.index or 0, True)   # start from a clean mark
     try:
         ops_gnn._pybind.set_wait_polls(0)
         csr_spmm(*dev, "sum")                                 # returns: the launch ends by itself

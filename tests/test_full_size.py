@@ -132,6 +132,7 @@ def test_config5_attention_rows_against_oracle(cuda_device):
     logits = ops_gnn.sddmm_csr(indptr, indices, left, right, "add", "u", "v")
     alpha = ops_gnn.scatter_softmax(torch.nn.functional.leaky_relu(logits, 0.2), rows, 0, nodes)
     out = ops_gnn.bspmm(indptr, indices, x, "mul", "sum", rhs=alpha.unsqueeze(-1))
+    fused = ops_gnn.gat_aggregate(indptr, indices, x, left, right, 0.2, edge_rows=rows)   # the same layer in two launches
     flat = x.view(nodes, heads * width)
     for first, last in _row_ranges(indptr, SAMPLE_EDGES // 2):
         ptr, local_col, (lo, hi), (x_rows, right_rows) = _local_graph(indptr, indices, first, last, flat, right)
@@ -144,6 +145,8 @@ def test_config5_attention_rows_against_oracle(cuda_device):
         magnitude = torch.zeros_like(want).index_add_(0, local_rows, terms.abs()).clamp(min=1.0)
         error = (out[first:last].cpu().double() - want).abs() / magnitude
         assert float(error.max()) <= 1e-5, f"aggregated features, rows [{first}, {last}): error {float(error.max()):.3g}"
+        error = (fused[first:last].cpu().double() - want).abs() / magnitude
+        assert float(error.max()) <= 1e-5, f"fused layer, rows [{first}, {last}): error {float(error.max()):.3g}"
 
 
 def test_config4_spmm_checksums(cuda_device):

@@ -115,6 +115,15 @@ def test_convert_fixtures():
         assert_same(oracle.ptr2ind_oracle(c["ptr"], c["ind"].numel()), c["ind"], "round trip")
 
 
+def test_gather_fixtures():
+    """gather_csr / gather_coo: the golden file's own known-answer table (every dtype it lists) and seeded cases."""
+    for i, c in enumerate(load_golden("gather")):
+        got = oracle.gather_csr_oracle(c["src"], c["indptr"])
+        assert_same(got, c["out"], f"case {i} gather_csr {c['src'].dtype} {tuple(c['src'].shape)}")
+        if "index" in c:
+            assert_same(oracle.gather_coo_oracle(c["src"], c["index"]), c["out"], f"case {i} gather_coo")
+
+
 # ---- known-answer vectors written in the reference's tests and docs ---------------------------------------------------
 def test_ind2ptr_documented_example():
     # python/ops_gnn/ind2ptr.py:48-52 of the reference
