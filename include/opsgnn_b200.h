@@ -221,9 +221,10 @@ OPSGNN_API int opsgnn_sddmm_csr_static(const OpsgnnSddmmDesc* desc, const void* 
  *   lse[r, h]   = log sum_{e in row r} exp(logit[e, h])            (-inf for a row without edges)
  *   out[r, h, :] = sum_{e in row r} exp(logit[e, h] - lse[r, h]) * x[col(e), h, :]
  * The reference has no such entry point: it composes the layer from sddmm_csr, leaky_relu, scatter_softmax and
- * spmm / bspmm (python/ops_gnn/spmm.py:148-208, 283-289) and writes the [E, H] logits and weights (and, in the spmm
- * fallback, the [E, H, D] messages) to memory.  Two calls: opsgnn_attention_lse (edge list + the [N, H] halves only),
- * then opsgnn_attention_aggregate (the weighted bulk instance of the CSR engine, weights formed in the gather ring).
+ * spmm / bspmm (python/ops_gnn/spmm.py:148-208, 283-289) and writes the [E, H] logits, their LeakyReLU, the softmax
+ * weights (and, in the spmm fallback, the [E, H, D] messages) to memory.  Two calls: opsgnn_attention_lse reads the edge
+ * list and the [N, H] halves and writes the logits [E, H] once together with lse; opsgnn_attention_aggregate (the weighted
+ * bulk instance of the CSR engine) reads the logits once and forms every weight exp(logit - lse) in the gather ring.
  * fp32 only.  The aggregation needs heads * width a multiple of 256, heads a multiple of 4 and at most 21, width a
  * multiple of 4 and 16-byte aligned right / x / out; other shapes return OPSGNN_ERR_UNSUPPORTED (compose the layer
  * from the four operators instead).
@@ -240,15 +241,17 @@ typedef struct OpsgnnAttentionDesc {
 } OpsgnnAttentionDesc;
 
 OPSGNN_API int opsgnn_attention_lse_workspace_bytes(const OpsgnnAttentionDesc* desc, int64_t* bytes);
-/* lse[rows, H] from edge_rows[nnz] (the CSR row of every edge, i.e. ptr2ind of the pointers), col[nnz], left[rows, H],
- * right[src_rows, H].  Deterministic: partial states of rows that span 32-edge chunks are folded in chunk order. */
+/* logits[nnz, H] and lse[rows, H] from edge_rows[nnz] (the CSR row of every edge, i.e. ptr2ind of the pointers), col[nnz],
+ * left[rows, H], right[src_rows, H].  Deterministic: partial states of rows that span 32-edge chunks are folded in chunk
+ * order (a row spanning more than 32 chunk boundaries by one thread block, in a fixed order). */
 OPSGNN_API int opsgnn_attention_lse(const OpsgnnAttentionDesc* desc, const void* edge_rows, const void* col, const float* left,
-                                    const float* right, float* lse, void* workspace, int64_t workspace_bytes, void* stream);
+                                    const float* right, float* logits, float* lse, void* workspace, int64_t workspace_bytes,
+                                    void* stream);
 /* out[rows, H * D]; plan and workspace are those of opsgnn_csr_reduce for a descriptor with feat = H * D,
  * value_width = H, fp32 in and out, sum (opsgnn_csr_plan_bytes / opsgnn_csr_reduce_workspace_bytes). */
-OPSGNN_API int opsgnn_attention_aggregate(const OpsgnnAttentionDesc* desc, const void* ptr, const void* col, const float* left,
-                                          const float* right, const float* lse, const void* x, void* out, const void* plan,
-                                          void* workspace, int64_t workspace_bytes, void* stream);
+OPSGNN_API int opsgnn_attention_aggregate(const OpsgnnAttentionDesc* desc, const void* ptr, const void* col, const float* logits,
+                                          const float* lse, const void* x, void* out, const void* plan, void* workspace,
+                                          int64_t workspace_bytes, void* stream);
 
 /* dvalue[e, w] = sum_b sum_k mat[b, col[e], k] * grad[b, row(e), k]  (w = 0 when width == 1, else k).
  * Replaces TorchSparseSpmmValueGrad (csrc/npu/torch_sparse_spmm/op_kernel/arch35/torch_sparse_spmm_kernel.h:326-395).
@@ -279,6 +282,12 @@ OPSGNN_API int opsgnn_permute_values(const int64_t* perm, const void* value, voi
  * One pass that serves the bounds checks of the grouped-softmax and scatter wrappers
  * (python/ops_gnn/_grouped_softmax.py:67-79, python/ops_gnn/scatter.py:347-361).  index_type I32/I64. */
 OPSGNN_API int opsgnn_index_stats(const void* index, int index_type, int64_t n, int64_t* stats, void* stream);
+/* longest[0] = rows of the largest group of a non-decreasing label vector: the longest run of equal consecutive values of
+ * index[0..n) or, with perm (int64, may be NULL), of index[perm[0]], index[perm[1]], ...  Meaningless when that sequence
+ * is not sorted.  Lets the grouped-softmax planner pick the single-read kernel; the reference has no sortedness
+ * specialisation (scatter_softmax_kernel_phase.h:126-279 runs three atomic phases for every index). */
+OPSGNN_API int opsgnn_index_longest_run(const void* index, int index_type, const int64_t* perm, int64_t n, int64_t* longest,
+                                        void* stream);
 
 /* out[i, :] = src[index[i], :] for rows of `row_bytes` bytes (a multiple of 16; src and every segment base 16-byte
  * aligned), with the output cut into `segments` (1..OPSGNN_GATHER_MAX_SEGMENTS) consecutive pieces: segment s holds

@@ -205,22 +205,18 @@ int PrepareReduce(const OpsgnnCsrReduceDesc* desc, const void* ptr, const void* 
     return OPSGNN_OK;
 }
 
-int RunAttention(const OpsgnnCsrReduceDesc& desc, const void* ptr, const void* col, const float* left, const float* right,
-                 const float* lse, float slope, const void* x, void* out, const void* plan, void* workspace,
-                 int64_t workspace_bytes, void* stream)
+int RunAttention(const OpsgnnCsrReduceDesc& desc, const void* ptr, const void* col, const float* logits, const float* lse,
+                 const void* x, void* out, const void* plan, void* workspace, int64_t workspace_bytes, void* stream)
 {
     Params p{};
     bool launch = false;
-    // `right` stands in for the weight operand: one value per (source row, head) instead of one per (edge, head)
-    int status = PrepareReduce(&desc, ptr, col, right, x, out, nullptr, plan, workspace, workspace_bytes, &p, &launch);
+    // the logits take the place of the per-(edge, head) weights; the kernel turns them into exp(logit - lse[row])
+    int status = PrepareReduce(&desc, ptr, col, logits, x, out, nullptr, plan, workspace, workspace_bytes, &p, &launch);
     if (status != OPSGNN_OK || !launch) {
         return status;
     }
     p.attention = 1;
-    p.att_left = left;
-    p.att_right = right;
     p.att_lse = lse;
-    p.att_slope = slope;
     cudaStream_t s = AsStream(stream);
     OPSGNN_CUDA_TRY(cudaMemsetAsync(p.status, 0, sizeof(unsigned long long), s));
     return RunSpmmF32(p, desc.ptr_type == OPSGNN_I64, kSum, s);

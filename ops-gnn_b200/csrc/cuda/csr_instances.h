@@ -19,9 +19,8 @@ int RunSegmentOther(const Params& p, int dtype, bool ptr64, int kind, cudaStream
 
 // Weighted bulk instance in attention mode (csr_abi.cu): the weight of an edge is formed from per-node halves and the
 // row's log-sum-exp instead of being read from memory.
-int RunAttention(const OpsgnnCsrReduceDesc& desc, const void* ptr, const void* col, const float* left, const float* right,
-                 const float* lse, float slope, const void* x, void* out, const void* plan, void* workspace,
-                 int64_t workspace_bytes, void* stream);
+int RunAttention(const OpsgnnCsrReduceDesc& desc, const void* ptr, const void* col, const float* logits, const float* lse,
+                 const void* x, void* out, const void* plan, void* workspace, int64_t workspace_bytes, void* stream);
 
 }  // namespace csr
 }  // namespace opsgnn

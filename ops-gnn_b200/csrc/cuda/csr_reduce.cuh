@@ -75,14 +75,10 @@ struct Params {
     int64_t val_width;  // weights per edge
     int64_t val_group;  // wide == 2: consecutive features that share a weight (feat / val_width)
     int lanes_per_row;  // narrow instance: lanes that share one gathered row (a power of two below 32)
-    // Attention mode of the weighted bulk instance (fp32): the weight of edge e and feature group h is not read from
-    // `val` but formed from per-node halves, w = exp(leaky_relu(att_left[row, h] + att_right[col(e), h]) - att_lse[row, h]),
-    // i.e. the softmax over the row's edges given its log-sum-exp.  `att_right` rows (val_width values) are gathered
-    // into the weight slots of the ring by one more bulk copy per edge; att_left / att_lse are read once per row.
-    const float* att_left;
-    const float* att_right;
+    // Attention mode of the weighted bulk instance (fp32): `val` holds one LOGIT per (edge, feature group) and the weight
+    // is formed on the fly, w = exp(val[e, h] - att_lse[row, h]): the softmax over the row's edges given the row's
+    // log-sum-exp, which is read once per row.  The softmax weights themselves are never in memory.
     const float* att_lse;
-    float att_slope;
     int attention;
 };
 
@@ -668,17 +664,11 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
         }
         const int n = (j1 - first < eb) ? j1 - first : eb;
         const int st = b % kBulkStages;
-        bool gather_weights = false;
-        if constexpr (kAttention) {
-            gather_weights = p.attention != 0;
-        }
         if (lane == 0) {
             if constexpr (GENERAL) {
                 MbarExpectTx(bar_addr + st * 8, static_cast<uint32_t>(n) * (seg_bytes + weight_row_bytes));
-                if (!gather_weights) {
-                    BulkLoad(weight_addr + static_cast<uint32_t>(st * kBulkWeightBytes), val + (a0 + first) * p.val_width,
-                             static_cast<uint32_t>(n) * weight_row_bytes, bar_addr + st * 8);
-                }
+                BulkLoad(weight_addr + static_cast<uint32_t>(st * kBulkWeightBytes), val + (a0 + first) * p.val_width,
+                         static_cast<uint32_t>(n) * weight_row_bytes, bar_addr + st * 8);
             } else {
                 MbarExpectTx(bar_addr + st * 8, static_cast<uint32_t>(n) * seg_bytes);
             }
@@ -697,23 +687,14 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
             if (OPSGNN_GUARD(4, static_cast<int64_t>(s_col[first + r]) * K + kbase + TILE - 1, p.src_rows * K + TILE)) {
                 BulkLoad(ring_addr + static_cast<uint32_t>(st * kBulkStageBytes + r * row_bytes),
                          mat + (static_cast<int64_t>(s_col[first + r]) * K32 + kbase), seg_bytes, bar_addr + st * 8);
-                if constexpr (kAttention) {
-                    if (gather_weights) {  // the column-side halves of this edge's logits, beside its row
-                        BulkLoad(weight_addr + static_cast<uint32_t>(st * kBulkWeightBytes) + static_cast<uint32_t>(r) * weight_row_bytes,
-                                 p.att_right + static_cast<int64_t>(s_col[first + r]) * p.val_width, weight_row_bytes,
-                                 bar_addr + st * 8);
-                    }
-                }
             }
         }
     };
-    // Attention mode: per-row constants of this lane's feature groups (row-side half of the logit, log-sum-exp).
-    float att_bias[NV];
+    // Attention mode: the log-sum-exp of the current row for this lane's feature groups.
     float att_norm[NV];
     int att_row = -1;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
-        att_bias[v] = 0.0f;
         att_norm[v] = 0.0f;
     }
     int batch_id = 0;
@@ -805,10 +786,8 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
                             w = Widen<A, T>(weight_ring[(batch_id % kBulkStages) * (kBulkWeightBytes / static_cast<int>(sizeof(T))) +
                                                         t * static_cast<int>(p.val_width) + static_cast<int>(group_of[v])]);
                             if constexpr (kAttention) {
-                                if (p.attention) {  // staged value = column-side half of the logit
-                                    float logit = static_cast<float>(w) + att_bias[v];
-                                    logit = logit > 0.0f ? logit : logit * p.att_slope;
-                                    w = static_cast<A>(__expf(logit - att_norm[v]));
+                                if (p.attention) {  // the staged value is the edge's logit
+                                    w = static_cast<A>(__expf(static_cast<float>(w) - att_norm[v]));
                                 }
                             }
                         } else if constexpr (GENERAL) {
@@ -869,7 +848,6 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
                     const int64_t at = (row0 + i) * p.val_width;
 #pragma unroll
                     for (int v = 0; v < NV; ++v) {
-                        att_bias[v] = __ldg(p.att_left + at + group_of[v]);
                         att_norm[v] = __ldg(p.att_lse + at + group_of[v]);
                     }
                 }

@@ -173,6 +173,40 @@ __global__ void StatsKernel(const IndexT* __restrict__ index, int64_t n, int64_t
     }
 }
 
+// Longest run of equal consecutive values of a NON-DECREASING index (the largest group of a sorted label vector): every
+// run start finds its end by a binary search for the first larger value.  On an index that is not sorted the result means
+// nothing (the search still ends).
+template <class IndexT>
+__global__ void LongestRunKernel(const IndexT* __restrict__ index, const int64_t* __restrict__ perm, int64_t n,
+                                 int64_t* __restrict__ longest)
+{
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    long long best = 0;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const long long v = index[perm != nullptr ? perm[i] : i];
+        if (i > 0 && static_cast<long long>(index[perm != nullptr ? perm[i - 1] : i - 1]) == v) {
+            continue;  // not a run start
+        }
+        int64_t lo = i + 1, hi = n;  // first position whose value exceeds v
+        while (lo < hi) {
+            const int64_t mid = (lo + hi) >> 1;
+            if (static_cast<long long>(index[perm != nullptr ? perm[mid] : mid]) <= v) {
+                lo = mid + 1;
+            } else {
+                hi = mid;
+            }
+        }
+        best = (lo - i) > best ? (lo - i) : best;
+    }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const long long other = __shfl_xor_sync(0xffffffffu, best, offset);
+        best = other > best ? other : best;
+    }
+    if ((threadIdx.x & 31) == 0 && best > 0) {
+        atomicMax(reinterpret_cast<long long*>(longest), best);
+    }
+}
+
 // ---- SpMM edge-value gradient --------------------------------------------------------------------------------------------
 // One warp per edge: lanes stride over the features (coalesced reads of the dense row and the gradient row), a shuffle
 // tree finishes the dot product.  With one weight per feature the lanes write their products directly.
@@ -335,6 +369,27 @@ extern "C" int opsgnn_index_stats(const void* index, int index_type, int64_t n, 
             StatsKernel<int64_t><<<grid, kThreads, 0, s>>>(static_cast<const int64_t*>(index), n, stats);
         } else if (index_type == OPSGNN_I32) {
             StatsKernel<int32_t><<<grid, kThreads, 0, s>>>(static_cast<const int32_t*>(index), n, stats);
+        } else {
+            return OPSGNN_ERR_UNSUPPORTED;
+        }
+    }
+    return LaunchStatus();
+}
+
+extern "C" int opsgnn_index_longest_run(const void* index, int index_type, const int64_t* perm, int64_t n, int64_t* longest,
+                                        void* stream)
+{
+    if (longest == nullptr || n < 0 || (n > 0 && index == nullptr)) {
+        return OPSGNN_ERR_INVALID;
+    }
+    cudaStream_t s = AsStream(stream);
+    OPSGNN_CUDA_TRY(cudaMemsetAsync(longest, 0, sizeof(int64_t), s));
+    if (n > 0) {
+        const unsigned grid = StreamGrid(n, 4);
+        if (index_type == OPSGNN_I64) {
+            LongestRunKernel<int64_t><<<grid, kThreads, 0, s>>>(static_cast<const int64_t*>(index), perm, n, longest);
+        } else if (index_type == OPSGNN_I32) {
+            LongestRunKernel<int32_t><<<grid, kThreads, 0, s>>>(static_cast<const int32_t*>(index), perm, n, longest);
         } else {
             return OPSGNN_ERR_UNSUPPORTED;
         }

@@ -1,7 +1,7 @@
 // Launch planner of the fused graph-attention aggregation (no counterpart in the reference, which composes the layer
 // from sddmm_csr, leaky_relu, scatter_softmax and spmm: python/ops_gnn/spmm.py:148-208, 283-289).  Two native calls on the
-// current stream: the per-row log-sum-exp of the edge logits, then the aggregation whose weights are formed in the
-// gather ring.  Returns (out, lse); lse is what a backward pass needs to rebuild the weights.
+// current stream: the edge logits and their per-row log-sum-exp, then the aggregation whose weights exp(logit - lse) are
+// formed in the gather ring.  Returns (out, lse); lse is what a backward pass needs to rebuild the weights.
 #include <pybind11/pybind11.h>
 
 #include "ops.h"
@@ -59,9 +59,10 @@ std::tuple<at::Tensor, at::Tensor> GatAggregate(const at::Tensor& indptr, const 
     int64_t bytes = 0;
     CheckStatus(opsgnn_attention_lse_workspace_bytes(&desc, &bytes), api);
     auto lse_scratch = Scratch(bytes, out);
+    auto logits = at::empty({edges, heads}, x.options());  // written once, read once; never the softmax weights
     CheckStatus(opsgnn_attention_lse(&desc, erow.const_data_ptr(), col.const_data_ptr(), lc.const_data_ptr<float>(),
-                                     rc.const_data_ptr<float>(), lse.data_ptr<float>(), lse_scratch.data_ptr(), lse_scratch.numel(),
-                                     CurrentStream(out)),
+                                     rc.const_data_ptr<float>(), logits.data_ptr<float>(), lse.data_ptr<float>(),
+                                     lse_scratch.data_ptr(), lse_scratch.numel(), CurrentStream(out)),
                 api);
     OpsgnnCsrReduceDesc reduce{};
     reduce.rows = rows;
@@ -78,10 +79,9 @@ std::tuple<at::Tensor, at::Tensor> GatAggregate(const at::Tensor& indptr, const 
     CheckStatus(opsgnn_csr_reduce_workspace_bytes(&reduce, &bytes), api);
     auto scratch = Scratch(bytes, out);
     at::Tensor plan = CsrPlan(ptr, rows, edges);
-    const int status = opsgnn_attention_aggregate(&desc, ptr.const_data_ptr(), col.const_data_ptr(), lc.const_data_ptr<float>(),
-                                                  rc.const_data_ptr<float>(), lse.const_data_ptr<float>(), xc.const_data_ptr(),
-                                                  out.data_ptr(), plan.const_data_ptr(), scratch.data_ptr(), scratch.numel(),
-                                                  CurrentStream(out));
+    const int status = opsgnn_attention_aggregate(&desc, ptr.const_data_ptr(), col.const_data_ptr(), logits.const_data_ptr<float>(),
+                                                  lse.const_data_ptr<float>(), xc.const_data_ptr(), out.data_ptr(),
+                                                  plan.const_data_ptr(), scratch.data_ptr(), scratch.numel(), CurrentStream(out));
     TORCH_CHECK(status != OPSGNN_ERR_UNSUPPORTED, api,
                 ": unsupported shape for the fused kernel (needs heads * width a multiple of 256, heads a multiple of 4 and at "
                 "most 21, width a multiple of 4); compose the layer from sddmm_csr, scatter_softmax and bspmm instead");

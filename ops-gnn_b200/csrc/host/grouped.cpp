@@ -14,11 +14,13 @@
 namespace opsgnn {
 namespace {
 
-// What the planner knows about a label vector, derived once per (tensor, version, write clock): is it sorted, how long
-// is its longest group, and - for an unsorted vector with short groups only - the stable permutation that sorts it.
+// What the planner knows about a label vector, derived once per (tensor, version, write clock): its value range, whether
+// it is sorted, how long its longest group is, and - for an unsorted vector with short groups only - the stable
+// permutation that sorts it.
 struct IndexFacts {
+    int64_t low = 0, high = -1;
     bool sorted = false;
-    int64_t longest = 0;   // rows of the largest group
+    int64_t longest = 0;   // rows of the largest group; valid when `measured`
     at::Tensor perm;       // int64 stable argsort, defined only when !sorted and longest <= OPSGNN_GROUPED_SHORT_GROUP
     bool measured = false; // longest (and perm) were derived; false for an unsorted vector nobody asked to sort yet
 };
@@ -29,10 +31,10 @@ struct SortedEntry {
 std::mutex g_sorted_mutex;
 std::list<SortedEntry> g_sorted;
 
-// One statistics kernel and a 24-byte read on a miss, plus - to learn the longest group - a run-length pass over the
-// (sorted) labels; an unsorted vector is argsorted once and the permutation kept.  Nothing on a hit.  The facts are
-// reused under the rules of TensorKey (identity, version, layout and the write clock): a stale "sorted" would send an
-// unsorted index down the sorted path.
+// Miss: one statistics kernel and one run-length kernel, read back together (32 bytes, one synchronisation); an unsorted
+// vector that should be sorted costs an argsort and a second run-length pass.  Hit: nothing.  The facts are reused under
+// the rules of TensorKey (identity, version, layout and the write clock): a stale "sorted" would send an unsorted index
+// down the sorted path.
 IndexFacts FactsOf(const at::Tensor& index, bool want_permutation)
 {
     auto key = TensorKey::Of(index);
@@ -45,21 +47,29 @@ IndexFacts FactsOf(const at::Tensor& index, bool want_permutation)
         }
     }
     IndexFacts facts;
-    auto stats = at::empty({3}, index.options().dtype(at::kLong));
-    CheckStatus(opsgnn_index_stats(index.const_data_ptr(), DtypeId(index.scalar_type(), "grouped"), index.numel(),
-                                   stats.data_ptr<int64_t>(), CurrentStream(index)),
+    const int type = DtypeId(index.scalar_type(), "grouped");
+    auto stats = at::empty({4}, index.options().dtype(at::kLong));
+    CheckStatus(opsgnn_index_stats(index.const_data_ptr(), type, index.numel(), stats.data_ptr<int64_t>(), CurrentStream(index)),
                 "grouped");
-    facts.sorted = stats[2].item<int64_t>() == 1;
-    at::Tensor ordered = index;
-    at::Tensor perm;
-    if (!facts.sorted && want_permutation) {
-        perm = at::argsort(index, /*stable=*/true, /*dim=*/0, /*descending=*/false);
-        ordered = index.index_select(0, perm);
-    }
-    if (facts.sorted || want_permutation) {
-        auto runs = at::unique_consecutive(ordered, /*return_inverse=*/false, /*return_counts=*/true);
-        facts.longest = std::get<2>(runs).numel() > 0 ? std::get<2>(runs).max().item<int64_t>() : 0;
-        if (!facts.sorted && facts.longest <= OPSGNN_GROUPED_SHORT_GROUP) {
+    CheckStatus(opsgnn_index_longest_run(index.const_data_ptr(), type, nullptr, index.numel(), stats.data_ptr<int64_t>() + 3,
+                                         CurrentStream(index)),
+                "grouped");
+    auto host = stats.cpu();
+    const int64_t* values = host.const_data_ptr<int64_t>();
+    facts.low = values[0];
+    facts.high = values[1];
+    facts.sorted = values[2] == 1;
+    if (facts.sorted) {
+        facts.longest = values[3];
+        facts.measured = true;
+    } else if (want_permutation) {
+        at::Tensor perm = at::argsort(index, /*stable=*/true, /*dim=*/0, /*descending=*/false);
+        auto longest = at::empty({1}, index.options().dtype(at::kLong));
+        CheckStatus(opsgnn_index_longest_run(index.const_data_ptr(), type, perm.const_data_ptr<int64_t>(), index.numel(),
+                                             longest.data_ptr<int64_t>(), CurrentStream(index)),
+                    "grouped");
+        facts.longest = longest.item<int64_t>();
+        if (facts.longest <= OPSGNN_GROUPED_SHORT_GROUP) {
             facts.perm = perm;
         }
         facts.measured = true;
@@ -219,6 +229,21 @@ at::Tensor scatter_logsumexp_backward(const at::Tensor& src, const at::Tensor& o
     return Backward(&src, out, grad_out, index, dim, dim_size, OPSGNN_GROUPED_LOGSUMEXP, "scatter_logsumexp");
 }
 
+// (minimum, maximum, sorted, longest group) of a label vector for the Python front-ends: the same cached facts the
+// forward planner reads a moment later, so validating the range costs no second pass.
+std::tuple<int64_t, int64_t, bool, int64_t> index_facts(const at::Tensor& index, bool want_permutation)
+{
+    TORCH_CHECK(index.defined() && index.device().is_cuda() && index.dim() == 1 && index.is_contiguous() &&
+                    (index.scalar_type() == at::kInt || index.scalar_type() == at::kLong),
+                "index_facts: index must be a contiguous 1-D int32/int64 CUDA tensor");
+    c10::cuda::CUDAGuard guard(index.device());
+    if (index.numel() == 0) {
+        return {0, -1, true, 0};
+    }
+    const IndexFacts facts = FactsOf(index, want_permutation);
+    return {facts.low, facts.high, facts.sorted, facts.longest};
+}
+
 void ClearSortedIndexCache()
 {
     std::lock_guard<std::mutex> lock(g_sorted_mutex);
@@ -238,6 +263,10 @@ namespace py = pybind11;
 void BindGrouped(py::module_& m)
 {
     using namespace opsgnn;
+    m.def("index_facts", Scoped(&index_facts), py::arg("index"), py::arg("want_permutation") = true,
+          "(minimum, maximum, sorted, rows of the largest group) of a contiguous label vector; cached per tensor like the "
+          "other facts, and shared with the grouped-softmax planners",
+          py::call_guard<py::gil_scoped_release>());
     m.def("scatter_softmax_forward", opsgnn::Scoped(&scatter_softmax_forward), py::arg("src"), py::arg("index"), py::arg("dim"),
           py::arg("dim_size"), "Grouped softmax forward on CUDA", py::call_guard<py::gil_scoped_release>());
     m.def("scatter_softmax_backward", opsgnn::Scoped(&scatter_softmax_backward), py::arg("out"), py::arg("grad_out"), py::arg("index"),

@@ -66,6 +66,7 @@ std::tuple<at::Tensor, at::Tensor> scatter_forward(at::Tensor src, at::Tensor in
                                                    int64_t reduce, bool has_out, int64_t hot_target);
 
 // grouped softmax family (grouped.cpp)
+std::tuple<int64_t, int64_t, bool, int64_t> index_facts(const at::Tensor& index, bool want_permutation);
 at::Tensor scatter_softmax_forward(const at::Tensor& src, const at::Tensor& index, int64_t dim, int64_t dim_size);
 at::Tensor scatter_softmax_backward(const at::Tensor& out, const at::Tensor& grad_out, const at::Tensor& index,
                                     int64_t dim, int64_t dim_size);

@@ -30,6 +30,7 @@ EXPORTS = (
     "opsgnn_attention_lse_workspace_bytes", "opsgnn_attention_lse", "opsgnn_attention_aggregate",
     "opsgnn_gather_rows", "opsgnn_gather_expand",
     "opsgnn_ind2ptr", "opsgnn_ptr2ind", "opsgnn_csr_validate", "opsgnn_permute_values", "opsgnn_index_stats",
+    "opsgnn_index_longest_run",
     "opsgnn_scatter_workspace_bytes", "opsgnn_scatter",
     "opsgnn_grouped_workspace_bytes", "opsgnn_grouped_forward", "opsgnn_grouped_forward_permuted", "opsgnn_grouped_backward",
 )
@@ -95,15 +96,16 @@ _PROTOTYPES = {
                                    POINTER(c_void_p), c_int, c_void_p]),
     "opsgnn_attention_lse_workspace_bytes": (c_int, [POINTER(AttentionDesc), POINTER(c_int64)]),
     "opsgnn_attention_lse": (c_int, [POINTER(AttentionDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                     c_int64, c_void_p]),
+                                     c_void_p, c_int64, c_void_p]),
     "opsgnn_attention_aggregate": (c_int, [POINTER(AttentionDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                           c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+                                           c_void_p, c_void_p, c_int64, c_void_p]),
     "opsgnn_gather_expand": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "opsgnn_ind2ptr": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
     "opsgnn_ptr2ind": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
     "opsgnn_csr_validate": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "opsgnn_permute_values": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "opsgnn_index_stats": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p]),
+    "opsgnn_index_longest_run": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
     "opsgnn_scatter_workspace_bytes": (c_int, [POINTER(ScatterDesc), POINTER(c_int64)]),
     "opsgnn_scatter": (c_int, [POINTER(ScatterDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                c_void_p]),

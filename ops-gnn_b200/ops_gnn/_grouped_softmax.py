@@ -44,8 +44,10 @@ def check_inputs(op: str, src: torch.Tensor, index: torch.Tensor, dim: int) -> N
 
 
 def index_bounds(index: torch.Tensor) -> Tuple[int, int]:
-    """(minimum, maximum) of a non-empty index through one fused device pass."""
-    low, high, _ = _pybind.index_stats(index).tolist()
+    """(minimum, maximum) of a non-empty index.  One device pass whose facts (range, sortedness, largest group) the
+    native planner reuses a moment later, as long as no other tensor operation runs in between."""
+    labels = index if index.is_contiguous() else index.contiguous()
+    low, high, _, _ = _pybind.index_facts(labels, True)
     return low, high
 
 
@@ -95,6 +97,7 @@ def build_autograd(op_name: str):
                 return torch.zeros_like(upstream), None, None, None
             return backward(out, upstream, labels, ctx.dim, ctx.groups), None, None, None
 
+    _Grouped.native_name = op_name
     _Grouped.__name__ = _Grouped.__qualname__ = f"_{op_name}"
     return _Grouped
 
@@ -107,4 +110,8 @@ def run(op: str, function, src, index, dim: int, dim_size: Optional[int]) -> tor
     dim = normalize_dim(dim, src.dim())
     check_inputs(op, src, index, dim)
     groups = resolve_groups(index, dim_size)
+    if not (torch.is_grad_enabled() and src.requires_grad) and src.numel() and src.is_contiguous() and index.is_contiguous():
+        # Nothing to differentiate: call the planner directly.  (An autograd node or a needless `.contiguous()` is a
+        # tensor operation, and any tensor operation makes the planner re-derive the index facts cached just above.)
+        return getattr(_pybind, f"{function.native_name}_forward")(src, index, dim, groups)
     return function.apply(src, index, dim, groups)

@@ -11,7 +11,8 @@ from .ptr2ind import ptr2ind
 def gat_aggregate(indptr: torch.Tensor, indices: torch.Tensor, x: torch.Tensor, left: torch.Tensor, right: torch.Tensor,
                   negative_slope: float = 0.2, edge_rows: Optional[torch.Tensor] = None,
                   return_lse: bool = False):
-    """One GAT layer over a CSR graph (rows = destination nodes) without any ``[E, H]`` tensor in memory.
+    """One GAT layer over a CSR graph (rows = destination nodes) in two launches; of the per-edge tensors only the logits
+    are written (once) and read (once), the LeakyReLU output and the softmax weights never exist in memory.
 
     ``logit[e, h] = leaky_relu(left[row(e), h] + right[indices[e], h])``; the weights are the softmax of the logits over
     the edges of each row, per head; ``out[r, h, :] = sum_e weight[e, h] * x[indices[e], h, :]``.  ``x`` is ``[N, H, D]``,
