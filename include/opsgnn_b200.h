@@ -65,6 +65,10 @@ extern "C" {
 /* strict compare against a +/-finite-max seed: NaN and values not better than
  * the seed never win; an unbeaten seed gives 0 (test/segment_coo/arch35/golden.py:42-58,132-148). */
 #define OPSGNN_EXTREMUM_SEEDED 2
+/* scatter's rule (test/scatter/arch35/golden.py:85-124, csrc/npu/scatter/op_kernel/arch35/scatter_kernel_minmax.h:116-147):
+ * non-strict compare against the +/-finite-max seed, so the LAST edge among ties wins; NaN and values beyond the seed
+ * (an infinity on the wrong side) never win; an unbeaten seed gives 0 and arg = arg_none. */
+#define OPSGNN_EXTREMUM_SEEDED_LAST 3
 
 OPSGNN_API const char* opsgnn_status_string(int status);
 /* Number of SMs of the current device (replaces ResolveAivCoreNum,
@@ -242,7 +246,7 @@ typedef struct OpsgnnAttentionDesc {
 
 OPSGNN_API int opsgnn_attention_lse_workspace_bytes(const OpsgnnAttentionDesc* desc, int64_t* bytes);
 /* logits[nnz, H] and lse[rows, H] from edge_rows[nnz] (the CSR row of every edge, i.e. ptr2ind of the pointers), col[nnz],
- * left[rows, H], right[src_rows, H].  Deterministic: partial states of rows that span 32-edge chunks are folded in chunk
+ * left[rows, H], right[src_rows, H].  Deterministic: partial states of rows that span 128-edge chunks are folded in chunk
  * order (a row spanning more than 32 chunk boundaries by one thread block, in a fixed order). */
 OPSGNN_API int opsgnn_attention_lse(const OpsgnnAttentionDesc* desc, const void* edge_rows, const void* col, const float* left,
                                     const float* right, float* logits, float* lse, void* workspace, int64_t workspace_bytes,

@@ -28,7 +28,8 @@ namespace opsgnn {
 namespace attention {
 
 constexpr int kThreads = 256;
-constexpr int kChunk = 32;
+constexpr int kChunk = 128;
+constexpr int kStep = 8;  // edges whose loads are in flight together in one thread
 
 struct LseParams {
     const void* edge_rows;
@@ -73,22 +74,22 @@ template <class IndexT> __global__ void __launch_bounds__(kThreads) EdgeLogitLse
     float m = -INFINITY, s = 0.0f;
     bool first_done = false;
     float* state = p.bound_state + (chunk * 2) * p.heads * 2 + head * 2;
-    for (int64_t base = e0; base < e1; base += 4) {
-        int64_t r[4], c[4];
-        float v[4];
+    for (int64_t base = e0; base < e1; base += kStep) {
+        int64_t r[kStep], c[kStep];
+        float v[kStep];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kStep; ++u) {
             const int64_t e = base + u < e1 ? base + u : e1 - 1;
             r[u] = static_cast<int64_t>(__ldg(edge_rows + e));
             c[u] = static_cast<int64_t>(__ldg(col + e));
             c[u] = c[u] < 0 ? 0 : (c[u] >= p.src_rows ? p.src_rows - 1 : c[u]);  // validated upstream; never fault
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kStep; ++u) {
             v[u] = __ldg(p.right + c[u] * p.heads + head);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < kStep; ++u) {
             if (base + u >= e1) {
                 break;
             }
@@ -128,7 +129,7 @@ template <class IndexT> __global__ void __launch_bounds__(kThreads) EdgeLogitLse
     }
 }
 
-// One thread per (boundary slot, head): the slot that opens a run of equal rows folds the run in slot order.  A run
+// One thread per boundary slot: the slot that opens a run of equal rows folds the run in slot order, head by head.  A run
 // longer than kShortRun slots (a hub row that spans hundreds of chunks) would make that one thread a serial chain of
 // dependent loads, so its opener only records the slot; LongRunKernel folds those runs with a whole thread block each.
 constexpr int kShortRun = 32;
@@ -136,11 +137,9 @@ constexpr int kMaxLongRuns = 1 << 16;
 
 __global__ void __launch_bounds__(kThreads) MergeBoundaryKernel(const LseParams p)
 {
-    const int64_t thread = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-    const int64_t slot = thread / p.lanes;
-    const int head = static_cast<int>(thread - slot * p.lanes);
+    const int64_t slot = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
     const int64_t slots = p.chunks * 2;
-    if (slot >= slots || head >= p.heads) {
+    if (slot >= slots) {
         return;
     }
     const int64_t row = p.bound_row[slot];
@@ -155,16 +154,13 @@ __global__ void __launch_bounds__(kThreads) MergeBoundaryKernel(const LseParams 
         return;  // not the opener of its run
     }
     if (slot + kShortRun < slots && p.bound_row[slot + kShortRun] == row) {  // rows are sorted: the run reaches that far
-        if (head == 0) {
-            const unsigned long long at = atomicAdd(reinterpret_cast<unsigned long long*>(p.long_runs), 1ULL);
-            if (at < kMaxLongRuns) {
-                p.long_runs[1 + at] = slot;
-            }
+        const unsigned long long at = atomicAdd(reinterpret_cast<unsigned long long*>(p.long_runs), 1ULL);
+        if (at < kMaxLongRuns) {
+            p.long_runs[1 + at] = slot;
         }
         return;
     }
-    float m = p.bound_state[(slot * p.heads + head) * 2];
-    float s = p.bound_state[(slot * p.heads + head) * 2 + 1];
+    int64_t last = slot;  // the run is [slot, last]; short, so its end is found first and the heads walk it afterwards
     for (int64_t next = slot + 1; next < slots; ++next) {
         const int64_t other = p.bound_row[next];
         if (other < 0) {
@@ -173,13 +169,23 @@ __global__ void __launch_bounds__(kThreads) MergeBoundaryKernel(const LseParams 
         if (other != row) {
             break;
         }
-        csr::LseMerge(m, s, p.bound_state[(next * p.heads + head) * 2], p.bound_state[(next * p.heads + head) * 2 + 1]);
+        last = next;
     }
-    p.lse[row * p.heads + head] = s == 0.0f ? m : m + __logf(s);
+    for (int head = 0; head < p.heads; ++head) {
+        float m = p.bound_state[(slot * p.heads + head) * 2];
+        float s = p.bound_state[(slot * p.heads + head) * 2 + 1];
+        for (int64_t next = slot + 1; next <= last; ++next) {
+            if (p.bound_row[next] == row) {
+                csr::LseMerge(m, s, p.bound_state[(next * p.heads + head) * 2], p.bound_state[(next * p.heads + head) * 2 + 1]);
+            }
+        }
+        p.lse[row * p.heads + head] = s == 0.0f ? m : m + __logf(s);
+    }
 }
 
-// One thread block per long run: kThreads / lanes slot-walkers per head stride over the run's slots, then fold their
-// states through shared memory in a fixed order (walker 0, 1, 2, ...), so the result does not depend on scheduling.
+// One thread block per long run: walker w (a warp lane group of `lanes` threads, one head each) takes slots
+// slot + w, slot + w + walkers, ...; the walkers' states are then folded through shared memory in walker order, so the
+// result does not depend on scheduling.  The run's length is found once by a binary search (rows are sorted).
 __global__ void __launch_bounds__(kThreads) LongRunKernel(const LseParams p)
 {
     __shared__ float s_m[kThreads];
@@ -193,14 +199,22 @@ __global__ void __launch_bounds__(kThreads) LongRunKernel(const LseParams p)
     for (int64_t k = blockIdx.x; k < count; k += gridDim.x) {
         const int64_t slot = p.long_runs[1 + k];
         const int64_t row = p.bound_row[slot];
+        // A chunk inside a long run holds only this row: its first slot carries the row, its last slot is absent (-1).
+        // The run ends at the first slot whose row is larger; absent slots are skipped by looking at even slots only.
+        int64_t lo = (slot + 2) / 2, hi = p.chunks;  // chunk indices: first chunk whose first row exceeds `row`
+        while (lo < hi) {
+            const int64_t mid = (lo + hi) >> 1;
+            if (p.bound_row[mid * 2] <= row) {
+                lo = mid + 1;
+            } else {
+                hi = mid;
+            }
+        }
+        const int64_t end = lo * 2;  // slots [slot, end) may belong to the run; the last chunk before `end` may end with another row
         float m = -INFINITY, s = 0.0f;
         if (head < p.heads) {
-            for (int64_t next = slot + walker; next < slots; next += walkers) {
-                const int64_t other = p.bound_row[next];
-                if (other > row) {
-                    break;
-                }
-                if (other == row) {
+            for (int64_t next = slot + walker; next < end && next < slots; next += walkers) {
+                if (p.bound_row[next] == row) {
                     csr::LseMerge(m, s, p.bound_state[(next * p.heads + head) * 2], p.bound_state[(next * p.heads + head) * 2 + 1]);
                 }
             }
@@ -308,9 +322,9 @@ extern "C" int opsgnn_attention_lse(const OpsgnnAttentionDesc* desc, const void*
     } else {
         attention::EdgeLogitLseKernel<int32_t><<<grid, attention::kThreads, 0, s>>>(p);
     }
-    const unsigned merge_grid = static_cast<unsigned>(CeilDiv(p.chunks * 2 * p.lanes, attention::kThreads));
+    const unsigned merge_grid = static_cast<unsigned>(CeilDiv(p.chunks * 2, attention::kThreads));
     attention::MergeBoundaryKernel<<<merge_grid, attention::kThreads, 0, s>>>(p);
-    attention::LongRunKernel<<<static_cast<unsigned>(SmCount()), attention::kThreads, 0, s>>>(p);
+    attention::LongRunKernel<<<static_cast<unsigned>(SmCount()) * 4, attention::kThreads, 0, s>>>(p);
     return LaunchStatus();
 }
 

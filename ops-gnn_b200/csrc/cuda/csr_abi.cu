@@ -65,7 +65,7 @@ int CheckDesc(const OpsgnnCsrReduceDesc* d)
     if (d->src_rows > 2147483647LL || d->feat > 2147483647LL) {
         return OPSGNN_ERR_LIMIT;  // staged column ids are 32-bit
     }
-    if (d->extremum < OPSGNN_EXTREMUM_IGNORE_NAN || d->extremum > OPSGNN_EXTREMUM_SEEDED) {
+    if (d->extremum < OPSGNN_EXTREMUM_IGNORE_NAN || d->extremum > OPSGNN_EXTREMUM_SEEDED_LAST) {
         return OPSGNN_ERR_INVALID;
     }
     return OPSGNN_OK;

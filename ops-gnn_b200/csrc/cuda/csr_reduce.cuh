@@ -151,6 +151,8 @@ __device__ __forceinline__ void ExtremumOffer(A& acc, I& arg, A v, I where, int 
         take = !IsNan(v) && (arg < 0 || better);
     } else if (rule == OPSGNN_EXTREMUM_PROPAGATE_NAN) {
         take = arg < 0 || better || (IsNan(v) && !IsNan(acc));
+    } else if (rule == OPSGNN_EXTREMUM_SEEDED_LAST) {
+        take = is_min ? (v <= acc) : (v >= acc);  // later edges are offered later: the last of equal values stays
     } else {
         take = better;
     }
@@ -163,7 +165,7 @@ __device__ __forceinline__ void ExtremumOffer(A& acc, I& arg, A v, I where, int 
 // Seed of the "seeded" rule: the finite extreme of the storage dtype T, held in the accumulator type.
 template <class A, class T> __device__ __forceinline__ A ExtremumSeed(int is_min, int rule)
 {
-    if (rule == OPSGNN_EXTREMUM_SEEDED) {
+    if (rule == OPSGNN_EXTREMUM_SEEDED || rule == OPSGNN_EXTREMUM_SEEDED_LAST) {
         return is_min ? static_cast<A>(Limits<T>::Max()) : static_cast<A>(Limits<T>::Lowest());
     }
     return A(0);
@@ -239,7 +241,8 @@ __device__ __forceinline__ void ExtremumMerge(A& acc, I& arg, A other, I other_a
         return;
     }
     const bool better = is_min ? (other < acc) : (other > acc);
-    if (better || (other == acc && other_arg < arg)) {
+    const bool tie_goes_to_other = rule == OPSGNN_EXTREMUM_SEEDED_LAST ? other_arg > arg : other_arg < arg;
+    if (better || (other == acc && tie_goes_to_other)) {
         acc = other;
         arg = other_arg;
     }
@@ -904,12 +907,12 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
                         consume(tt + grp);
                     }
                 }
-            } else if constexpr (BULK && EB > 4) {
+            } else if constexpr (BULK && EB > 6) {
                 for (int t = t_begin; t < t_end; ++t) {
                     consume(t);
                 }
             } else
-            switch (t_begin) {  // register path and four-row bulk stages: slots are compile-time, offsets immediates
+            switch (t_begin) {  // register path and bulk stages of up to six rows: slots are compile-time, offsets immediates
                 OPSGNN_SLOT(0)
                 OPSGNN_SLOT(1)
                 OPSGNN_SLOT(2)

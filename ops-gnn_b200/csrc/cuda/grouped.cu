@@ -286,14 +286,28 @@ template <class T, int VEC> __global__ void __launch_bounds__(kThreads) SegmentS
                 }
                 continue;
             }
-            Pack<T, VEC> kept[kCachedRows];
+            Pack<T, VEC> kept[kCachedRows];   // the group's first rows stay in registers for the second sweep
             float m[VEC], s[VEC];
 #pragma unroll
             for (int c = 0; c < VEC; ++c) {
                 m[c] = -INFINITY;
                 s[c] = 0.0f;
             }
-            // first sweep: online (maximum, scaled sum); the first kCachedRows rows stay in registers
+            auto offer = [&](const Pack<T, VEC>& packed) {
+                float x[VEC];
+                Unpack<float, T, VEC>(packed, x);
+#pragma unroll
+                for (int c = 0; c < VEC; ++c) {
+                    if (x[c] > m[c]) {
+                        s[c] = s[c] * __expf(m[c] - x[c]) + 1.0f;
+                        m[c] = x[c];
+                    } else {
+                        s[c] += __expf(x[c] == m[c] ? 0.0f : x[c] - m[c]);
+                    }
+                }
+            };
+            // first sweep: online (maximum, scaled sum), kCachedRows rows per step with every load issued before the
+            // first use, so a long group is as many round trips as it has steps, not as it has rows
 #pragma unroll
             for (int k = 0; k < kCachedRows; ++k) {
                 if (first + k < last) {
@@ -304,30 +318,22 @@ template <class T, int VEC> __global__ void __launch_bounds__(kThreads) SegmentS
 #pragma unroll
             for (int k = 0; k < kCachedRows; ++k) {
                 if (first + k < last) {
-                    float x[VEC];
-                    Unpack<float, T, VEC>(kept[k], x);
-#pragma unroll
-                    for (int c = 0; c < VEC; ++c) {
-                        if (x[c] > m[c]) {
-                            s[c] = s[c] * __expf(m[c] - x[c]) + 1.0f;
-                            m[c] = x[c];
-                        } else {
-                            s[c] += __expf(x[c] == m[c] ? 0.0f : x[c] - m[c]);
-                        }
-                    }
+                    offer(kept[k]);
                 }
             }
-            for (int64_t e = first + kCachedRows; e < last; ++e) {
-                const int64_t row = perm != nullptr ? perm[e] : e;
-                float x[VEC];
-                Unpack<float, T, VEC>(LoadGather<T, VEC>(src + row * p.after + offset), x);
+            for (int64_t base = first + kCachedRows; base < last; base += kCachedRows) {
+                Pack<T, VEC> more[kCachedRows];
 #pragma unroll
-                for (int c = 0; c < VEC; ++c) {
-                    if (x[c] > m[c]) {
-                        s[c] = s[c] * __expf(m[c] - x[c]) + 1.0f;
-                        m[c] = x[c];
-                    } else {
-                        s[c] += __expf(x[c] == m[c] ? 0.0f : x[c] - m[c]);
+                for (int k = 0; k < kCachedRows; ++k) {
+                    if (base + k < last) {
+                        const int64_t row = perm != nullptr ? perm[base + k] : base + k;
+                        more[k] = LoadGather<T, VEC>(src + row * p.after + offset);
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < kCachedRows; ++k) {
+                    if (base + k < last) {
+                        offer(more[k]);
                     }
                 }
             }
@@ -354,9 +360,22 @@ template <class T, int VEC> __global__ void __launch_bounds__(kThreads) SegmentS
                     finish(kept[k], perm != nullptr ? perm[first + k] : first + k);
                 }
             }
-            for (int64_t e = first + kCachedRows; e < last; ++e) {
-                const int64_t row = perm != nullptr ? perm[e] : e;
-                finish(LoadGather<T, VEC>(src + row * p.after + offset), row);
+            for (int64_t base = first + kCachedRows; base < last; base += kCachedRows) {  // beyond the registers: L1 / L2
+                Pack<T, VEC> more[kCachedRows];
+                int64_t rows[kCachedRows];
+#pragma unroll
+                for (int k = 0; k < kCachedRows; ++k) {
+                    if (base + k < last) {
+                        rows[k] = perm != nullptr ? perm[base + k] : base + k;
+                        more[k] = LoadGather<T, VEC>(src + rows[k] * p.after + offset);
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < kCachedRows; ++k) {
+                    if (base + k < last) {
+                        finish(more[k], rows[k]);
+                    }
+                }
             }
         }
     }

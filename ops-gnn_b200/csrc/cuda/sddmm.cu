@@ -12,6 +12,8 @@
 // Algorithmic bytes per launch (dot): nnz*(sizeof(index) + F*sizeof(T) + sizeof(T)) + rows*(sizeof(index) + F*sizeof(T)).
 #include <utility>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace opsgnn {
@@ -501,7 +503,8 @@ namespace {
 constexpr int64_t kStaticPlanEntries = OPSGNN_SDDMM_STATIC_MAX_EDGES / opsgnn::sddmm::kEdgesPerCta + 1;
 static __device__ __align__(256) int64_t g_static_plan[kStaticPlanEntries];
 constexpr int kMaxDevices = 64;
-void* g_static_plan_address[kMaxDevices] = {nullptr};  // device address of g_static_plan, per device ordinal
+// device address of g_static_plan, per device ordinal; atomic because first calls on one device may come from several host threads
+std::atomic<void*> g_static_plan_address[kMaxDevices];
 }  // namespace
 
 extern "C" int opsgnn_sddmm_csr_static(const OpsgnnSddmmDesc* desc, const void* indptr, const void* indices,
@@ -518,13 +521,15 @@ extern "C" int opsgnn_sddmm_csr_static(const OpsgnnSddmmDesc* desc, const void* 
     if (device < 0 || device >= kMaxDevices) {
         return OPSGNN_ERR_LIMIT;
     }
-    if (g_static_plan_address[device] == nullptr) {
+    void* plan_address = g_static_plan_address[device].load(std::memory_order_acquire);
+    if (plan_address == nullptr) {
         // In host code `g_static_plan` names a host-side stand-in, not device memory: the address a kernel may use
         // has to be looked up, with the owning device current (it is: cudaGetDevice above).
         void* address = nullptr;
         OPSGNN_CUDA_TRY(cudaGetSymbolAddress(&address, g_static_plan));
-        g_static_plan_address[device] = address;
+        g_static_plan_address[device].store(address, std::memory_order_release);
+        plan_address = address;
     }
-    return opsgnn_sddmm_csr(desc, indptr, indices, lhs, rhs, out, g_static_plan_address[device],
+    return opsgnn_sddmm_csr(desc, indptr, indices, lhs, rhs, out, plan_address,
                             kStaticPlanEntries * static_cast<int64_t>(sizeof(int64_t)), stream);
 }

@@ -173,7 +173,19 @@ int64_t DeviceStallCount(int device, bool synchronize);
 // device-to-host read on a miss.
 int CsrFacts(const at::Tensor& ptr, const std::optional<at::Tensor>& col, int64_t rows, int64_t cols, int64_t nnz);
 void ClearCsrFactsCache();
-void ClearSortedIndexCache();                          // grouped.cpp: the sortedness facts of label vectors
+// What the planners know about a 1-D label vector (grouped.cpp), derived once per (tensor, version, write clock): its
+// value range, whether it is non-decreasing, the rows of its largest group and - for an unsorted vector somebody asked
+// to sort - the stable permutation that sorts it.  Miss: two small kernels and one 32-byte read (plus an argsort and a
+// second run-length pass for the permutation).  Hit: nothing.
+struct LabelFacts {
+    int64_t low = 0, high = -1;
+    bool sorted = false;
+    int64_t longest = 0;    // rows of the largest group; valid when `measured`
+    at::Tensor perm;        // int64 stable argsort; defined only when !sorted and a permutation was asked for
+    bool measured = false;  // longest (and perm) were derived
+};
+LabelFacts LabelFactsOf(const at::Tensor& index, bool want_permutation);
+void ClearSortedIndexCache();                          // grouped.cpp: the facts of label vectors
 int64_t SortedIndexCacheSize();
 std::tuple<int64_t, int64_t, int64_t> NativeCacheSizes();  // plans, validation facts, sortedness facts
 

@@ -14,19 +14,9 @@
 namespace opsgnn {
 namespace {
 
-// What the planner knows about a label vector, derived once per (tensor, version, write clock): its value range, whether
-// it is sorted, how long its longest group is, and - for an unsorted vector with short groups only - the stable
-// permutation that sorts it.
-struct IndexFacts {
-    int64_t low = 0, high = -1;
-    bool sorted = false;
-    int64_t longest = 0;   // rows of the largest group; valid when `measured`
-    at::Tensor perm;       // int64 stable argsort, defined only when !sorted and longest <= OPSGNN_GROUPED_SHORT_GROUP
-    bool measured = false; // longest (and perm) were derived; false for an unsorted vector nobody asked to sort yet
-};
 struct SortedEntry {
     TensorKey index;
-    IndexFacts facts;
+    LabelFacts facts;
 };
 std::mutex g_sorted_mutex;
 std::list<SortedEntry> g_sorted;
@@ -35,7 +25,9 @@ std::list<SortedEntry> g_sorted;
 // vector that should be sorted costs an argsort and a second run-length pass.  Hit: nothing.  The facts are reused under
 // the rules of TensorKey (identity, version, layout and the write clock): a stale "sorted" would send an unsorted index
 // down the sorted path.
-IndexFacts FactsOf(const at::Tensor& index, bool want_permutation)
+}  // namespace
+
+LabelFacts LabelFactsOf(const at::Tensor& index, bool want_permutation)
 {
     auto key = TensorKey::Of(index);
     if (key) {
@@ -46,7 +38,7 @@ IndexFacts FactsOf(const at::Tensor& index, bool want_permutation)
             }
         }
     }
-    IndexFacts facts;
+    LabelFacts facts;
     const int type = DtypeId(index.scalar_type(), "grouped");
     auto stats = at::empty({4}, index.options().dtype(at::kLong));
     CheckStatus(opsgnn_index_stats(index.const_data_ptr(), type, index.numel(), stats.data_ptr<int64_t>(), CurrentStream(index)),
@@ -69,9 +61,7 @@ IndexFacts FactsOf(const at::Tensor& index, bool want_permutation)
                                              longest.data_ptr<int64_t>(), CurrentStream(index)),
                     "grouped");
         facts.longest = longest.item<int64_t>();
-        if (facts.longest <= OPSGNN_GROUPED_SHORT_GROUP) {
-            facts.perm = perm;
-        }
+        facts.perm = perm;
         facts.measured = true;
     } else {
         facts.longest = index.numel();  // unknown: treat as long
@@ -86,6 +76,8 @@ IndexFacts FactsOf(const at::Tensor& index, bool want_permutation)
     }
     return facts;
 }
+
+namespace {
 
 struct View {
     int64_t batch, dim_len, after;
@@ -138,9 +130,9 @@ at::Tensor Forward(const at::Tensor& src, const at::Tensor& index, int64_t dim, 
     const bool short_shape = mode != OPSGNN_GROUPED_LOGSUMEXP && v.batch == 1 && v.after % vec == 0 &&
                              reinterpret_cast<uintptr_t>(src.const_data_ptr()) % 16 == 0 &&
                              reinterpret_cast<uintptr_t>(out.data_ptr()) % 16 == 0;
-    IndexFacts facts;
+    LabelFacts facts;
     if (index.numel() > 0) {
-        facts = FactsOf(index, short_shape);
+        facts = LabelFactsOf(index, short_shape);
     }
     const bool short_groups = short_shape && facts.longest <= OPSGNN_GROUPED_SHORT_GROUP;
     OpsgnnGroupedDesc desc = MakeDesc(v, src, index, dim_size, mode, facts.sorted);
@@ -240,7 +232,7 @@ std::tuple<int64_t, int64_t, bool, int64_t> index_facts(const at::Tensor& index,
     if (index.numel() == 0) {
         return {0, -1, true, 0};
     }
-    const IndexFacts facts = FactsOf(index, want_permutation);
+    const LabelFacts facts = LabelFactsOf(index, want_permutation);
     return {facts.low, facts.high, facts.sorted, facts.longest};
 }
 

@@ -41,6 +41,46 @@ std::tuple<at::Tensor, at::Tensor> scatter_forward(at::Tensor src, at::Tensor in
     if (out.numel() == 0) {
         return {out, arg};
     }
+    // Extrema without atomics: sort the labels once (a stable argsort, cached with the other facts of the label
+    // vector), then one launch of the CSR reduce engine whose "columns" are the permutation - a gather is what it does
+    // best.  A stable sort keeps the source order inside a group, so "the last edge among ties" of the engine's
+    // seeded rule is the largest source position, which is what scatter reports
+    // (csrc/npu/scatter/op_kernel/arch35/scatter_kernel_minmax.h:116-147 of the reference does a second sweep for it).
+    // Floating dtypes, a compact index along the leading dimension, no caller-seeded output; the rest keeps the
+    // atomic kernels.
+    const bool floating = src.scalar_type() == at::kFloat || src.scalar_type() == at::kHalf || src.scalar_type() == at::kBFloat16;
+    if (extremum && floating && compact && before == 1 && !has_out && dim_len > 0 && after > 0 && dim_len < 2147483647LL) {
+        const LabelFacts facts = LabelFactsOf(index, true);
+        if (facts.low >= 0 && facts.high < out.size(dim) && (facts.sorted || facts.perm.defined())) {
+            const int64_t groups = out.size(dim);
+            at::Tensor ordered = facts.sorted ? index : index.index_select(0, facts.perm);
+            at::Tensor ptr = at::empty({groups + 1}, index.options());
+            CheckStatus(opsgnn_ind2ptr(ordered.const_data_ptr<int64_t>(), dim_len, ptr.data_ptr<int64_t>(), groups, CurrentStream(out)),
+                        "scatter");
+            CsrReduceCall call;
+            call.ptr = ptr;
+            if (!facts.sorted) {
+                call.col = facts.perm;
+            }
+            call.mat = src.view({dim_len, after});
+            call.out = out.view({groups, after});
+            call.arg = arg.view({groups, after});
+            call.rows = groups;
+            call.src_rows = dim_len;
+            call.feat = after;
+            call.nnz = dim_len;
+            call.arg_none = dim_len;
+            call.reduce = reduce == OPSGNN_SCATTER_MIN ? OPSGNN_REDUCE_MIN : OPSGNN_REDUCE_MAX;
+            call.extremum = OPSGNN_EXTREMUM_SEEDED_LAST;
+            RunCsrReduce(call, "scatter");
+            if (!facts.sorted) {
+                // positions are places in the sorted order: map them back to source positions (dim_len stays dim_len)
+                at::Tensor back = at::cat({facts.perm, at::full({1}, dim_len, facts.perm.options())});
+                arg.copy_(back.index_select(0, arg.view({-1})).view(arg.sizes()));
+            }
+            return {out, arg};
+        }
+    }
     OpsgnnScatterDesc desc{};
     desc.before = before;
     desc.dim_len = dim_len;

@@ -16,7 +16,7 @@ LIBRARY_PATH = os.path.join(_HERE, "sm100", "libopsgnn_b200.so")
 # dtype ids (include/opsgnn_b200.h)
 F32, F16, BF16, I8, I32, I64, U8, I16, F64 = range(9)
 REDUCE_SUM, REDUCE_MEAN, REDUCE_MIN, REDUCE_MAX, REDUCE_LOGSUMEXP = range(5)
-EXTREMUM_IGNORE_NAN, EXTREMUM_PROPAGATE_NAN, EXTREMUM_SEEDED = range(3)
+EXTREMUM_IGNORE_NAN, EXTREMUM_PROPAGATE_NAN, EXTREMUM_SEEDED, EXTREMUM_SEEDED_LAST = range(4)
 SDDMM_OPS = {"dot": 0, "add": 1, "sub": 2, "mul": 3, "div": 4, "copy_lhs": 5, "copy_rhs": 6}
 SCATTER_SUM, SCATTER_MUL, SCATTER_MEAN, SCATTER_MIN, SCATTER_MAX = range(5)
 GROUPED_SOFTMAX, GROUPED_LOG_SOFTMAX, GROUPED_LOGSUMEXP = range(3)

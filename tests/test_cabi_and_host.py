@@ -154,3 +154,20 @@ def test_device_selection(monkeypatch):
     monkeypatch.delenv("OPS_GNN_TARGET")
     if not torch.cuda.is_available():
         assert _device.select_target() == "sm100"
+
+
+def test_static_scratch_covers_its_stated_maximum():
+    """The built-in array of `opsgnn_sddmm_csr_static` must hold the plan of the largest call it accepts: the workspace
+    query for 2^24 edges gives the array's size (256 KiB + one entry), one edge more asks for more."""
+    import ctypes
+
+    from ops_gnn import _cabi
+
+    lib = _cabi.load()
+    size = ctypes.c_int64()
+    at_limit = _cabi.SddmmDesc(10, 1 << 24, 64, 10, 10, 0, 0, 2, _cabi.I64, _cabi.F32)
+    assert lib.opsgnn_sddmm_workspace_bytes(ctypes.byref(at_limit), ctypes.byref(size)) == 0
+    assert size.value == ((1 << 24) // 512 + 1) * 8
+    beyond = _cabi.SddmmDesc(10, (1 << 24) + 512, 64, 10, 10, 0, 0, 2, _cabi.I64, _cabi.F32)
+    assert lib.opsgnn_sddmm_workspace_bytes(ctypes.byref(beyond), ctypes.byref(size)) == 0
+    assert size.value > ((1 << 24) // 512 + 1) * 8

@@ -17,7 +17,7 @@ from conftest import requires_gpu
 pytestmark = requires_gpu
 
 
-def _graph(device, rows, seed):
+def _graph(device, rows, seed, index_dtype=torch.int64):
     gen = torch.Generator().manual_seed(seed)
     degree = torch.randint(0, 12, (rows,), generator=gen)
     degree[2] = 3000
@@ -26,14 +26,14 @@ def _graph(device, rows, seed):
     col = torch.randint(0, rows, (int(ptr[-1]),), generator=gen)
     lhs = torch.randn(rows, 64, generator=gen)
     rhs = torch.randn(rows, 64, generator=gen)
-    return [t.to(device) for t in (ptr, col, lhs, rhs)]
+    return [t.to(device) for t in (ptr.to(index_dtype), col.to(index_dtype), lhs, rhs)]
 
 
-def _run(lib, cabi, static, ptr, col, lhs, rhs):
+def _run(lib, cabi, static, ptr, col, lhs, rhs, op="dot"):
     nnz = col.numel()
-    desc = cabi.SddmmDesc(ptr.numel() - 1, nnz, lhs.size(1), lhs.size(0), rhs.size(0), cabi.SDDMM_OPS["dot"], 0, 2,
-                          cabi.I64, cabi.F32)
-    out = torch.full((nnz,), float("nan"), device=ptr.device)
+    desc = cabi.SddmmDesc(ptr.numel() - 1, nnz, lhs.size(1), lhs.size(0), rhs.size(0), cabi.SDDMM_OPS[op], 0, 2,
+                          cabi.torch_dtype_id(ptr.dtype), cabi.F32)
+    out = torch.full((nnz,) if op == "dot" else (nnz, lhs.size(1)), float("nan"), device=ptr.device)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     args = [ctypes.byref(desc)] + [ctypes.c_void_p(t.data_ptr()) for t in (ptr, col, lhs, rhs, out)]
     if static:
@@ -52,12 +52,21 @@ def test_static_scratch_matches_regular_entry_point(cuda_device):
     from ops_gnn import _cabi
 
     lib = _cabi.load()
-    for rows, seed in ((5000, 1), (1200, 2)):  # two calls in a row share the internal array
-        inputs = _graph(cuda_device, rows, seed)
-        regular = _run(lib, _cabi, False, *inputs)
-        fixed = _run(lib, _cabi, True, *inputs)
+    import oracle
+
+    # calls in a row share the internal array: two graph sizes, both index widths, the dot product and an elementwise op
+    for rows, seed, index_dtype, op in ((5000, 1, torch.int64, "dot"), (1200, 2, torch.int64, "dot"),
+                                        (3000, 3, torch.int32, "dot"), (2000, 4, torch.int32, "mul")):
+        inputs = _graph(cuda_device, rows, seed, index_dtype)
+        regular = _run(lib, _cabi, False, *inputs, op=op)
+        fixed = _run(lib, _cabi, True, *inputs, op=op)
         assert not torch.isnan(fixed).any()
         assert torch.equal(fixed, regular)
+        # third leg: the CPU oracle, so the entry point stands on its own
+        ptr, col, lhs, rhs = (t.cpu() for t in inputs)
+        want = oracle.sddmm_oracle(ptr, col, lhs.double(), rhs.double(), op, "u", "v")
+        scale = oracle.sddmm_oracle(ptr, col, lhs.double().abs(), rhs.double().abs(), op, "u", "v").clamp(min=1.0)
+        assert float(((fixed.cpu().double() - want).abs() / scale).max()) <= 1e-5, f"{op} against the oracle"
     too_many = _cabi.SddmmDesc(10, (1 << 24) + 1, 64, 10, 10, 0, 0, 2, _cabi.I64, _cabi.F32)
     status = lib.opsgnn_sddmm_csr_static(ctypes.byref(too_many), None, None, None, None, None, None)
     assert status == -4 and b"maximum" in lib.opsgnn_status_string(status)
