@@ -8,9 +8,10 @@
 // exp(x - lse) or x - lse.  src is read twice and out written once.
 // Forward, short groups (softmax / log-softmax, one batch, rows of whole 16-byte vectors, every group at most
 // OPSGNN_GROUPED_SHORT_GROUP rows - the planner knows that from a cached fact about the index): SegmentSoftmaxKernel.
-// A group of lanes owns a whole group of rows: it reads the rows once (the first eight stay in registers, longer
-// groups come back from L1 / L2), forms the log-sum-exp online and writes exp(x - lse) or x - lse straight away, so src
-// crosses DRAM once and out once: the algorithmic bytes.  With a permutation (a stable argsort of an UNSORTED index,
+// A group of lanes owns a whole group of rows: it reads the rows, forms the log-sum-exp online, reads them again - from
+// L1 / L2 now, the same lanes fetched them a moment ago - and writes exp(x - lse) or x - lse, so src crosses DRAM once
+// and out once: the algorithmic bytes.  (Keeping the first rows in registers instead cost 158 registers and two thirds
+// of the resident warps: 1.24 ms against 0.47 ms on the config-2 shape.)  With a permutation (a stable argsort of an UNSORTED index,
 // made and cached by the planner) the same kernel reads and writes row perm[e] instead of row e: the unsorted case
 // then needs no atomics and no fp32 scratch either.
 // Forward, unsorted index without a permutation: the reference's three phases on fp32 scratch of shape [batch, groups, after]:
@@ -257,9 +258,9 @@ template <class T, int VEC> __global__ void __launch_bounds__(kThreads) ApplyLse
 // lanes * VEC features is walked tile by tile.  Row e of the (sorted) sequence is row perm[e] of src and out when a
 // permutation is given.  Pseudo groups `groups` and `groups + 1` are the rows whose label lies below 0 or at / above
 // `groups` (they come first / last in the sorted order): their output is 0, as in the other paths.
-constexpr int kCachedRows = 8;
+constexpr int kCachedRows = 4;
 
-template <class T, int VEC> __global__ void __launch_bounds__(kThreads) SegmentSoftmaxKernel(
+template <class T, int VEC> __global__ void __launch_bounds__(kThreads, 3) SegmentSoftmaxKernel(
     const Params p, const int64_t* __restrict__ ptr, const int64_t* __restrict__ perm, int lanes)
 {
     const T* __restrict__ src = static_cast<const T*>(p.src);
@@ -286,54 +287,37 @@ template <class T, int VEC> __global__ void __launch_bounds__(kThreads) SegmentS
                 }
                 continue;
             }
-            Pack<T, VEC> kept[kCachedRows];   // the group's first rows stay in registers for the second sweep
             float m[VEC], s[VEC];
 #pragma unroll
             for (int c = 0; c < VEC; ++c) {
                 m[c] = -INFINITY;
                 s[c] = 0.0f;
             }
-            auto offer = [&](const Pack<T, VEC>& packed) {
-                float x[VEC];
-                Unpack<float, T, VEC>(packed, x);
-#pragma unroll
-                for (int c = 0; c < VEC; ++c) {
-                    if (x[c] > m[c]) {
-                        s[c] = s[c] * __expf(m[c] - x[c]) + 1.0f;
-                        m[c] = x[c];
-                    } else {
-                        s[c] += __expf(x[c] == m[c] ? 0.0f : x[c] - m[c]);
-                    }
-                }
-            };
             // first sweep: online (maximum, scaled sum), kCachedRows rows per step with every load issued before the
-            // first use, so a long group is as many round trips as it has steps, not as it has rows
-#pragma unroll
-            for (int k = 0; k < kCachedRows; ++k) {
-                if (first + k < last) {
-                    const int64_t row = perm != nullptr ? perm[first + k] : first + k;
-                    kept[k] = LoadGather<T, VEC>(src + row * p.after + offset);
-                }
-            }
-#pragma unroll
-            for (int k = 0; k < kCachedRows; ++k) {
-                if (first + k < last) {
-                    offer(kept[k]);
-                }
-            }
-            for (int64_t base = first + kCachedRows; base < last; base += kCachedRows) {
-                Pack<T, VEC> more[kCachedRows];
+            // first use, so a group costs as many round trips as it has steps, not as it has rows
+            for (int64_t base = first; base < last; base += kCachedRows) {
+                Pack<T, VEC> rows_in[kCachedRows];
 #pragma unroll
                 for (int k = 0; k < kCachedRows; ++k) {
                     if (base + k < last) {
                         const int64_t row = perm != nullptr ? perm[base + k] : base + k;
-                        more[k] = LoadGather<T, VEC>(src + row * p.after + offset);
+                        rows_in[k] = LoadGather<T, VEC>(src + row * p.after + offset);
                     }
                 }
 #pragma unroll
                 for (int k = 0; k < kCachedRows; ++k) {
                     if (base + k < last) {
-                        offer(more[k]);
+                        float x[VEC];
+                        Unpack<float, T, VEC>(rows_in[k], x);
+#pragma unroll
+                        for (int c = 0; c < VEC; ++c) {
+                            if (x[c] > m[c]) {
+                                s[c] = s[c] * __expf(m[c] - x[c]) + 1.0f;
+                                m[c] = x[c];
+                            } else {
+                                s[c] += __expf(x[c] == m[c] ? 0.0f : x[c] - m[c]);
+                            }
+                        }
                     }
                 }
             }
@@ -342,38 +326,30 @@ template <class T, int VEC> __global__ void __launch_bounds__(kThreads) SegmentS
             for (int c = 0; c < VEC; ++c) {
                 lse[c] = s[c] == 0.0f ? m[c] : m[c] + __logf(s[c]);
             }
-            // second sweep: the result; a group with a +inf member, only -inf members or a NaN is NaN throughout
-            auto finish = [&](const Pack<T, VEC>& packed, int64_t row) {
-                float x[VEC], y[VEC];
-                Unpack<float, T, VEC>(packed, x);
-#pragma unroll
-                for (int c = 0; c < VEC; ++c) {
-                    const float shifted = x[c] - lse[c];
-                    const float value = p.mode == OPSGNN_GROUPED_SOFTMAX ? __expf(shifted) : shifted;
-                    y[c] = isfinite(lse[c]) ? value : NAN;
-                }
-                StoreStream<T, VEC>(out + row * p.after + offset, Repack<T, float, VEC>(y));
-            };
-#pragma unroll
-            for (int k = 0; k < kCachedRows; ++k) {
-                if (first + k < last) {
-                    finish(kept[k], perm != nullptr ? perm[first + k] : first + k);
-                }
-            }
-            for (int64_t base = first + kCachedRows; base < last; base += kCachedRows) {  // beyond the registers: L1 / L2
-                Pack<T, VEC> more[kCachedRows];
-                int64_t rows[kCachedRows];
+            // second sweep: the rows come back from L1 / L2 (the same lanes read them a moment ago), the result goes out
+            // with streaming stores; a group with a +inf member, only -inf members or a NaN is NaN throughout
+            for (int64_t base = first; base < last; base += kCachedRows) {
+                Pack<T, VEC> rows_in[kCachedRows];
 #pragma unroll
                 for (int k = 0; k < kCachedRows; ++k) {
                     if (base + k < last) {
-                        rows[k] = perm != nullptr ? perm[base + k] : base + k;
-                        more[k] = LoadGather<T, VEC>(src + rows[k] * p.after + offset);
+                        const int64_t row = perm != nullptr ? perm[base + k] : base + k;
+                        rows_in[k] = LoadGather<T, VEC>(src + row * p.after + offset);
                     }
                 }
 #pragma unroll
                 for (int k = 0; k < kCachedRows; ++k) {
                     if (base + k < last) {
-                        finish(more[k], rows[k]);
+                        const int64_t row = perm != nullptr ? perm[base + k] : base + k;
+                        float x[VEC], y[VEC];
+                        Unpack<float, T, VEC>(rows_in[k], x);
+#pragma unroll
+                        for (int c = 0; c < VEC; ++c) {
+                            const float shifted = x[c] - lse[c];
+                            const float value = p.mode == OPSGNN_GROUPED_SOFTMAX ? __expf(shifted) : shifted;
+                            y[c] = isfinite(lse[c]) ? value : NAN;
+                        }
+                        StoreStream<T, VEC>(out + row * p.after + offset, Repack<T, float, VEC>(y));
                     }
                 }
             }
