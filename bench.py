@@ -213,7 +213,7 @@ def parse():
                         help="N > 1: the same for the host-buffer leg (measured at 4 GPUs: 272 ms per step with 1, 310 with 50)")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
-    parser.add_argument("--no-ops", action="store_true", help="skip the SDDMM / GAT legs (profiling runs)")
+    parser.add_argument("--no-ops", action="store_true", help="skip the SDDMM / GAT legs, single-GPU and sharded (profiling runs)")
     return parser.parse_args()
 
 
@@ -476,12 +476,19 @@ def main():
             "kernel": kernel + " (+ FixupKernel, 0.8 % of the step, inside the same timed region)",
         }
 
-    # ---- end to end through the public API with host buffers -----------------------------------------------------------
+    # ---- N > 1: the other sharded operators north_star names (SDDMM, GAT layer) ---------------------------------------------
     out = None
+    if distributed and not args.no_ops:
+        del sharded, local_x, x_block, local_ptr, local_col, my_ptr, my_col, my_val
+        sharded = local_x = x_block = None
+        torch.cuda.empty_cache()
+        result["ops"] = sharded_operators(dist, device, world, rank, max(3, min(args.steps, 10)))
+
+    # ---- end to end through the public API with host buffers -----------------------------------------------------------
     torch.cuda.empty_cache()
     if not args.no_e2e:
         if distributed:
-            del sharded, local_x, x_block
+            sharded = local_x = x_block = None
             torch.cuda.empty_cache()
             result["e2e"] = end_to_end_sharded(args, host_shard, nnz, dist, device, world)
         else:
@@ -506,6 +513,81 @@ def main():
     if distributed:
         dist.destroy_process_group()
     return 0
+
+
+def sharded_operators(dist, device, world, rank, steps):
+    """N > 1: `sddmm_csr` dot (BASELINE config 3) and the fused GAT layer (config 5) row-sharded over the ranks with the
+    needed-rows exchange (`HaloShardedSddmm`, `ShardedGatLayer(fused=True)`): ms per step (CUDA events, max over ranks)
+    and, for SDDMM, a check of every rank's first edges against a float64 product formed from the unsharded operands."""
+    import ops_gnn
+    from ops_gnn.distributed import HaloShardedSddmm, ShardedGatLayer, balanced_row_bounds, shard_csr
+
+    def timed(step):
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(steps):
+            result = step()
+        end.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([begin.elapsed_time(end) / steps], device=device)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), result
+
+    record = {}
+    scale = 21
+    nodes = 1 << scale
+    # ---- config 3: out[e] = <A[row e], B[col e]> -------------------------------------------------------------------------
+    indptr, indices = rmat_csr(scale, 32 * nodes, device, seed=20261125 + 3)
+    nnz = indices.numel()
+    gen = torch.Generator(device=device).manual_seed(20261125 + 3)
+    a = torch.randn(nodes, 64, device=device, generator=gen)
+    b = torch.randn(nodes, 64, device=device, generator=gen)
+    bounds = balanced_row_bounds(indptr, world, row_cost=1.0)
+    ptr, col, _ = shard_csr(indptr, indices, None, bounds[rank], bounds[rank + 1])
+    own = slice(bounds[rank], bounds[rank + 1])
+    probe = min(col.numel(), 1 << 18)
+    local_rows = ops_gnn.ptr2ind(ptr, col.numel())[:probe]
+    want = (a[own][local_rows].double() * b[col[:probe]].double()).sum(-1)
+    size = (a[own][local_rows].double().abs() * b[col[:probe]].double().abs()).sum(-1).clamp(min=1.0)
+    op = HaloShardedSddmm(ptr, col, bounds, 64, a.dtype, device)
+    a_block, b_block = a[own].contiguous(), op.own_block.copy_(b[own])
+    del a, b, indptr, indices
+    ms, dots = timed(lambda: op(a_block, b_block))
+    error = torch.tensor([float(((dots[:probe].double() - want).abs() / size).max()) if probe else 0.0], device=device)
+    dist.all_reduce(error, op=dist.ReduceOp.MAX)
+    record["sddmm_sharded"] = {"ms_per_step": ms, "nnz_per_s": nnz / (ms * 1e-3), "nnz": nnz,
+                               "parity_check": {"max_rel_err": float(error.item()), "tolerance": 1e-5,
+                                                "ok": bool(error.item() <= 1e-5), "edges_per_rank": probe}}
+    del op, a_block, b_block, dots, want, size
+    torch.cuda.empty_cache()
+    # ---- config 5: the GAT layer -------------------------------------------------------------------------------------------
+    heads, width = 8, 64
+    indptr, indices = rmat_csr(scale, 16 * nodes, device, seed=20261125 + 5)
+    rows = ops_gnn.ptr2ind(indptr, indices.numel())
+    loops = torch.arange(nodes, device=device)
+    keys = torch.unique(torch.cat([(rows << scale) | indices, (loops << scale) | loops]))
+    rows, indices = keys >> scale, keys & (nodes - 1)
+    indptr = ops_gnn.ind2ptr(rows, nodes)
+    del keys, loops, rows
+    gen = torch.Generator(device=device).manual_seed(20261125 + 5)
+    x = torch.randn(nodes, heads, width, device=device, generator=gen)
+    left = torch.randn(nodes, heads, device=device, generator=gen)
+    right = torch.randn(nodes, heads, device=device, generator=gen)
+    bounds = balanced_row_bounds(indptr, world, row_cost=4.0)
+    ptr, col, _ = shard_csr(indptr, indices, None, bounds[rank], bounds[rank + 1])
+    own = slice(bounds[rank], bounds[rank + 1])
+    layer = ShardedGatLayer(ptr, col, bounds, heads, width, x.dtype, device, fused=True)
+    blocks = (x[own].contiguous(), left[own].contiguous(), right[own].contiguous())
+    nnz = indices.numel()
+    del x, left, right, indptr, indices
+    ms, _ = timed(lambda: layer(*blocks))
+    record["gat_layer_sharded"] = {"ms_per_step": ms, "nnz": nnz, "form": "needed-rows exchange of x and right, then gat_aggregate"}
+    return record
 
 
 def other_operators(device, skip_cpu):

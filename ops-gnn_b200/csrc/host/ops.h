@@ -65,6 +65,9 @@ at::Tensor SddmmCsrForward(const at::Tensor& indptr, const at::Tensor& indices, 
 std::tuple<at::Tensor, at::Tensor> scatter_forward(at::Tensor src, at::Tensor index, int64_t dim, at::Tensor out,
                                                    int64_t reduce, bool has_out, int64_t hot_target);
 
+std::optional<std::tuple<at::Tensor, at::Tensor>> scatter_extremum_sorted(const at::Tensor& src, const at::Tensor& index,
+                                                                         int64_t length, bool is_min);
+
 // grouped softmax family (grouped.cpp)
 std::tuple<int64_t, int64_t, bool, int64_t> index_facts(const at::Tensor& index, bool want_permutation);
 at::Tensor scatter_softmax_forward(const at::Tensor& src, const at::Tensor& index, int64_t dim, int64_t dim_size);

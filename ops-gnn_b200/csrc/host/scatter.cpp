@@ -8,6 +8,57 @@
 
 namespace opsgnn {
 
+namespace {
+
+// Extrema without atomics: sort the labels once (a stable argsort, cached with the other facts of the label vector),
+// then one launch of the CSR reduce engine whose "columns" are the permutation - a gather is what it does best.  A
+// stable sort keeps the source order inside a group, so "the last edge among ties" of the engine's seeded rule is the
+// largest source position, which is what scatter reports (csrc/npu/scatter/op_kernel/arch35/scatter_kernel_minmax.h:
+// 116-147 of the reference does a second sweep for it).  Floating dtypes, a compact index along the leading dimension,
+// no caller-seeded output; returns false (nothing launched) for anything else, and the atomic kernels take over.
+// `out` is [groups, ...] contiguous, `arg` int64 of the same shape.
+bool SortedExtremum(const at::Tensor& src, const at::Tensor& index, const at::Tensor& out, const at::Tensor& arg, int64_t dim_len,
+                    int64_t after, bool is_min)
+{
+    const bool floating = src.scalar_type() == at::kFloat || src.scalar_type() == at::kHalf || src.scalar_type() == at::kBFloat16;
+    if (!floating || dim_len <= 0 || after <= 0 || dim_len >= 2147483647LL || out.numel() == 0) {
+        return false;
+    }
+    const int64_t groups = out.numel() / after;
+    const LabelFacts facts = LabelFactsOf(index, true);
+    if (facts.low < 0 || facts.high >= groups || !(facts.sorted || facts.perm.defined())) {
+        return false;
+    }
+    at::Tensor ordered = facts.sorted ? index : index.index_select(0, facts.perm);
+    at::Tensor ptr = at::empty({groups + 1}, index.options());
+    CheckStatus(opsgnn_ind2ptr(ordered.const_data_ptr<int64_t>(), dim_len, ptr.data_ptr<int64_t>(), groups, CurrentStream(out)),
+                "scatter");
+    CsrReduceCall call;
+    call.ptr = ptr;
+    if (!facts.sorted) {
+        call.col = facts.perm;
+    }
+    call.mat = src.view({dim_len, after});
+    call.out = out.view({groups, after});
+    call.arg = arg.view({groups, after});
+    call.rows = groups;
+    call.src_rows = dim_len;
+    call.feat = after;
+    call.nnz = dim_len;
+    call.arg_none = dim_len;
+    call.reduce = is_min ? OPSGNN_REDUCE_MIN : OPSGNN_REDUCE_MAX;
+    call.extremum = OPSGNN_EXTREMUM_SEEDED_LAST;
+    RunCsrReduce(call, "scatter");
+    if (!facts.sorted) {
+        // positions are places in the sorted order: map them back to source positions (dim_len stays dim_len)
+        at::Tensor back = at::cat({facts.perm, at::full({1}, dim_len, facts.perm.options())});
+        arg.copy_(back.index_select(0, arg.view({-1})).view(arg.sizes()));
+    }
+    return true;
+}
+
+}  // namespace
+
 std::tuple<at::Tensor, at::Tensor> scatter_forward(at::Tensor src, at::Tensor index, int64_t dim, at::Tensor out,
                                                    int64_t reduce, bool has_out, int64_t /*hot_target*/)
 {
@@ -41,45 +92,9 @@ std::tuple<at::Tensor, at::Tensor> scatter_forward(at::Tensor src, at::Tensor in
     if (out.numel() == 0) {
         return {out, arg};
     }
-    // Extrema without atomics: sort the labels once (a stable argsort, cached with the other facts of the label
-    // vector), then one launch of the CSR reduce engine whose "columns" are the permutation - a gather is what it does
-    // best.  A stable sort keeps the source order inside a group, so "the last edge among ties" of the engine's
-    // seeded rule is the largest source position, which is what scatter reports
-    // (csrc/npu/scatter/op_kernel/arch35/scatter_kernel_minmax.h:116-147 of the reference does a second sweep for it).
-    // Floating dtypes, a compact index along the leading dimension, no caller-seeded output; the rest keeps the
-    // atomic kernels.
-    const bool floating = src.scalar_type() == at::kFloat || src.scalar_type() == at::kHalf || src.scalar_type() == at::kBFloat16;
-    if (extremum && floating && compact && before == 1 && !has_out && dim_len > 0 && after > 0 && dim_len < 2147483647LL) {
-        const LabelFacts facts = LabelFactsOf(index, true);
-        if (facts.low >= 0 && facts.high < out.size(dim) && (facts.sorted || facts.perm.defined())) {
-            const int64_t groups = out.size(dim);
-            at::Tensor ordered = facts.sorted ? index : index.index_select(0, facts.perm);
-            at::Tensor ptr = at::empty({groups + 1}, index.options());
-            CheckStatus(opsgnn_ind2ptr(ordered.const_data_ptr<int64_t>(), dim_len, ptr.data_ptr<int64_t>(), groups, CurrentStream(out)),
-                        "scatter");
-            CsrReduceCall call;
-            call.ptr = ptr;
-            if (!facts.sorted) {
-                call.col = facts.perm;
-            }
-            call.mat = src.view({dim_len, after});
-            call.out = out.view({groups, after});
-            call.arg = arg.view({groups, after});
-            call.rows = groups;
-            call.src_rows = dim_len;
-            call.feat = after;
-            call.nnz = dim_len;
-            call.arg_none = dim_len;
-            call.reduce = reduce == OPSGNN_SCATTER_MIN ? OPSGNN_REDUCE_MIN : OPSGNN_REDUCE_MAX;
-            call.extremum = OPSGNN_EXTREMUM_SEEDED_LAST;
-            RunCsrReduce(call, "scatter");
-            if (!facts.sorted) {
-                // positions are places in the sorted order: map them back to source positions (dim_len stays dim_len)
-                at::Tensor back = at::cat({facts.perm, at::full({1}, dim_len, facts.perm.options())});
-                arg.copy_(back.index_select(0, arg.view({-1})).view(arg.sizes()));
-            }
-            return {out, arg};
-        }
+    if (extremum && !has_out && compact && before == 1 &&
+        SortedExtremum(src, index, out, arg, dim_len, after, reduce == OPSGNN_SCATTER_MIN)) {
+        return {out, arg};
     }
     OpsgnnScatterDesc desc{};
     desc.before = before;
@@ -100,12 +115,41 @@ std::tuple<at::Tensor, at::Tensor> scatter_forward(at::Tensor src, at::Tensor in
     return {out, arg};
 }
 
+// scatter min / max over a 1-D index along dimension 0 with no caller-provided output, outputs allocated HERE: the
+// Python front-end calls it right after reading the index facts, with no tensor operation in between, so the cached
+// permutation of an unsorted index is reused from call to call.  Returns nothing when the sorted path does not apply
+// (the front-end then takes scatter_forward).  Not part of the reference binding.
+std::optional<std::tuple<at::Tensor, at::Tensor>> scatter_extremum_sorted(const at::Tensor& src, const at::Tensor& index,
+                                                                         int64_t length, bool is_min)
+{
+    TORCH_CHECK(src.defined() && src.device().is_cuda() && index.defined() && index.device() == src.device(),
+                "scatter: src and index must be CUDA tensors on one GPU");
+    if (index.scalar_type() != at::kLong || index.dim() != 1 || src.dim() < 1 || index.numel() != src.size(0) ||
+        !src.is_contiguous() || !index.is_contiguous() || length <= 0) {
+        return std::nullopt;
+    }
+    c10::cuda::CUDAGuard guard(src.device());
+    auto shape = src.sizes().vec();
+    shape[0] = length;
+    at::Tensor out = at::empty(shape, src.options());
+    at::Tensor arg = at::empty(shape, src.options().dtype(at::kLong));
+    const int64_t after = Product(src.sizes(), 1, src.dim());
+    if (!SortedExtremum(src, index, out, arg, src.size(0), after, is_min)) {
+        return std::nullopt;
+    }
+    return std::make_tuple(out, arg);
+}
+
 }  // namespace opsgnn
 
 namespace py = pybind11;
 
 void BindScatter(py::module_& m)
 {
+    m.def("scatter_extremum_sorted", opsgnn::Scoped(&opsgnn::scatter_extremum_sorted), py::arg("src"), py::arg("index"),
+          py::arg("length"), py::arg("is_min"),
+          "scatter min / max along dim 0 through a cached stable argsort of the index (no atomics); None when it does not apply",
+          py::call_guard<py::gil_scoped_release>());
     m.def("scatter_forward", opsgnn::Scoped(&opsgnn::scatter_forward), py::arg("src"), py::arg("index"), py::arg("dim"), py::arg("out"),
           py::arg("reduce"), py::arg("has_out"), py::arg("hot_target") = -1,
           "torch_scatter-compatible forward reduction (CUDA)", py::call_guard<py::gil_scoped_release>());

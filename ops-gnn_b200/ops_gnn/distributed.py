@@ -299,23 +299,34 @@ class HaloShardedSddmm(HaloShardedSpmm):
 
 
 class ShardedGatLayer:
-    """A GAT-style attention layer over a row-sharded graph, composed from the sharded operators.
+    """A GAT-style attention layer over a row-sharded graph.
 
     Per head ``h``: ``logit[e, h] = left[row(e), h] + right[col(e), h]``, LeakyReLU, softmax over the edges of each
     destination row, ``out[r, h, :] = sum_e alpha[e, h] * x[col(e), h, :]``.  Rows are the shard's own, so the
     softmax needs no exchange; ``right`` (``[rows, heads]``) and ``x`` (``[rows, heads, width]``) go through the
-    needed-rows exchange, ``left`` is local.  The aggregation is the fused per-head weighted SpMM.
+    needed-rows exchange, ``left`` is local.
+
+    ``fused=False`` composes the layer from the sharded operators (sharded SDDMM ``add``, ``scatter_softmax``, fused
+    per-head aggregation).  ``fused=True`` exchanges ``right`` and ``x`` into their compact buffers and runs the local
+    layer as :func:`ops_gnn.gat_aggregate` (two launches, no ``[E, H]`` softmax tensor).
     """
 
     def __init__(self, rowptr, col, bounds: Sequence[int], heads: int, width: int, dtype, device, group=None,
-                 transport: str = "alltoall", negative_slope: float = 0.2):
+                 transport: str = "alltoall", negative_slope: float = 0.2, fused: bool = False):
         from .bspmm import bspmm
         from .ptr2ind import ptr2ind
         from .scatter_softmax import scatter_softmax
 
-        self.heads, self.width, self.slope = heads, width, negative_slope
+        self.heads, self.width, self.slope, self.fused = heads, width, negative_slope, fused
         self.rows = rowptr.numel() - 1
+        self.rowptr = rowptr
         self.edge_rows = ptr2ind(rowptr, col.numel())
+        if fused:
+            self.features = HaloShardedSpmm(rowptr, col, None, bounds, heads * width, dtype, device, group=group,
+                                            transport=transport, local_spmm=lambda *unused: None)
+            self.halves = HaloShardedSpmm(rowptr, col, None, bounds, heads, dtype, device, group=group,
+                                          transport=transport, local_spmm=lambda *unused: None)
+            return
         self.softmax = scatter_softmax
         self.logits = HaloShardedSddmm(rowptr, col, bounds, heads, dtype, device, group=group, transport=transport, op="add")
         self.aggregate = HaloShardedSpmm(
@@ -323,6 +334,14 @@ class ShardedGatLayer:
             local_spmm=lambda ptr, c, alpha, x: bspmm(ptr, c, x.view(-1, heads, width), "mul", "sum", rhs=alpha))
 
     def __call__(self, x_block: torch.Tensor, left_block: torch.Tensor, right_block: torch.Tensor) -> torch.Tensor:
+        if self.fused:
+            from .gat_aggregate import gat_aggregate
+
+            x_all = self.features.exchange(x_block.reshape(self.rows, self.heads * self.width))
+            right_all = self.halves.exchange(right_block)
+            out = gat_aggregate(self.rowptr, self.features.col, x_all.view(-1, self.heads, self.width), left_block, right_all,
+                                self.slope, edge_rows=self.edge_rows)
+            return out.view(self.rows, self.heads * self.width)
         scores = torch.nn.functional.leaky_relu(self.logits(left_block, right_block), self.slope)
         self.aggregate.value = self.softmax(scores, self.edge_rows, 0, self.rows).unsqueeze(-1)
         return self.aggregate(x_block.reshape(self.rows, self.heads * self.width))

@@ -111,6 +111,21 @@ def _initial_output(src: torch.Tensor, reduce: str, shape) -> torch.Tensor:
 
 def _scatter_forward(src: torch.Tensor, index: torch.Tensor, request: _Request):
     dim = _check(src, index, request)
+    if (request.out is None and request.reduce in ("min", "max") and dim == 0 and index.dim() == 1 and index.dtype == torch.int64
+            and src.dtype in (torch.float32, torch.float16, torch.bfloat16) and index.numel() == src.size(0) and src.numel() > 0
+            and src.is_contiguous() and index.is_contiguous()):
+        # Extrema over a 1-D index along the leading dimension: sorted once (a stable argsort the planner caches with the
+        # index's other facts) and reduced by the CSR engine, no atomics.  Nothing between the two native calls is a tensor
+        # operation, so back-to-back calls reuse the permutation.
+        low, high, _, _ = _pybind.index_facts(index, True)
+        if low < 0:
+            raise IndexError(f"index contains a negative value ({low})")
+        length = high + 1 if request.dim_size is None else request.dim_size
+        if high >= length:
+            raise IndexError(f"index value {high} is out of bounds for output size {length} at dimension {dim}")
+        done = _pybind.scatter_extremum_sorted(src, index, length, request.reduce == "min")
+        if done is not None:
+            return done
     try:
         expanded = broadcast(index, src, dim)
     except RuntimeError as exc:

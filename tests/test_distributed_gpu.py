@@ -88,6 +88,8 @@ def _worker(rank, world, port, result_dir):
     own = slice(bounds[rank], bounds[rank + 1])
     layer = ShardedGatLayer(ptr, c, bounds, heads, width, feats.dtype, device, transport="pull")
     results["gat"] = layer(feats[own].contiguous(), el[own].contiguous(), er[own].contiguous()).cpu()
+    fused_layer = ShardedGatLayer(ptr, c, bounds, heads, width, feats.dtype, device, transport="alltoall", fused=True)
+    results["gat_fused"] = fused_layer(feats[own].contiguous(), el[own].contiguous(), er[own].contiguous()).cpu()
     torch.cuda.synchronize()
     torch.save(results, os.path.join(result_dir, f"rank{rank}.pt"))
     dist.barrier()
@@ -133,6 +135,8 @@ def test_sharded_spmm_two_gpus(tmp_path):
     want_gat = ops_gnn.bspmm(rowptr, col, feats, "mul", "sum", rhs=alpha.unsqueeze(-1)).cpu()
     got_gat = torch.cat([p["gat"] for p in parts]).view(-1, heads, width)
     assert float((got_gat - want_gat).abs().max()) <= 2e-5 * max(float(want_gat.abs().max()), 1.0), "sharded GAT layer"
+    got_fused = torch.cat([p["gat_fused"] for p in parts]).view(-1, heads, width)
+    assert float((got_fused - want_gat).abs().max()) <= 2e-5 * max(float(want_gat.abs().max()), 1.0), "sharded fused GAT layer"
     sent = sum(p["alltoall_exchange"][0] for p in parts)
     received = sum(p["alltoall_exchange"][1] for p in parts)
     assert sent == received and 0 < received < x.size(0)
