@@ -247,7 +247,7 @@ typedef struct OpsgnnAttentionDesc {
 OPSGNN_API int opsgnn_attention_lse_workspace_bytes(const OpsgnnAttentionDesc* desc, int64_t* bytes);
 /* logits[nnz, H] and lse[rows, H] from edge_rows[nnz] (the CSR row of every edge, i.e. ptr2ind of the pointers), col[nnz],
  * left[rows, H], right[src_rows, H].  Deterministic: partial states of rows that span 128-edge chunks are folded in chunk
- * order (a row spanning more than 32 chunk boundaries by one thread block, in a fixed order). */
+ * order (a row spanning more than 4 chunk boundaries by one warp, in a fixed order). */
 OPSGNN_API int opsgnn_attention_lse(const OpsgnnAttentionDesc* desc, const void* edge_rows, const void* col, const float* left,
                                     const float* right, float* logits, float* lse, void* workspace, int64_t workspace_bytes,
                                     void* stream);

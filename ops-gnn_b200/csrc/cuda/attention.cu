@@ -56,7 +56,7 @@ __device__ __forceinline__ void Offer(float& m, float& s, float x)
     }
 }
 
-template <class IndexT> __global__ void __launch_bounds__(kThreads) EdgeLogitLseKernel(const LseParams p)
+template <class IndexT> __global__ void __launch_bounds__(kThreads, 4) EdgeLogitLseKernel(const LseParams p)
 {
     const int64_t thread = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
     const int64_t chunk = thread / p.lanes;
@@ -70,23 +70,25 @@ template <class IndexT> __global__ void __launch_bounds__(kThreads) EdgeLogitLse
     const int64_t e1 = (e0 + kChunk < p.nnz) ? e0 + kChunk : p.nnz;
     const int64_t first_row = static_cast<int64_t>(__ldg(edge_rows + e0));
     int64_t row = first_row;
-    float bias = __ldg(p.left + row * p.heads + head);
+    float bias = (row >= 0 && row < p.rows) ? __ldg(p.left + row * p.heads + head) : 0.0f;
     float m = -INFINITY, s = 0.0f;
     bool first_done = false;
     float* state = p.bound_state + (chunk * 2) * p.heads * 2 + head * 2;
     for (int64_t base = e0; base < e1; base += kStep) {
-        int64_t r[kStep], c[kStep];
+        int r[kStep], c[kStep];  // rows and columns fit 31 bits (checked by the entry point)
         float v[kStep];
 #pragma unroll
         for (int u = 0; u < kStep; ++u) {
             const int64_t e = base + u < e1 ? base + u : e1 - 1;
-            r[u] = static_cast<int64_t>(__ldg(edge_rows + e));
-            c[u] = static_cast<int64_t>(__ldg(col + e));
-            c[u] = c[u] < 0 ? 0 : (c[u] >= p.src_rows ? p.src_rows - 1 : c[u]);  // validated upstream; never fault
+            const int64_t row_id = static_cast<int64_t>(__ldg(edge_rows + e));
+            int64_t column = static_cast<int64_t>(__ldg(col + e));
+            column = column < 0 ? 0 : (column >= p.src_rows ? p.src_rows - 1 : column);  // validated upstream; never fault
+            r[u] = static_cast<int>(row_id < 0 ? -1 : (row_id >= p.rows ? p.rows : row_id));
+            c[u] = static_cast<int>(column);
         }
 #pragma unroll
         for (int u = 0; u < kStep; ++u) {
-            v[u] = __ldg(p.right + c[u] * p.heads + head);
+            v[u] = __ldg(p.right + static_cast<int64_t>(c[u]) * p.heads + head);
         }
 #pragma unroll
         for (int u = 0; u < kStep; ++u) {
@@ -132,7 +134,7 @@ template <class IndexT> __global__ void __launch_bounds__(kThreads) EdgeLogitLse
 // One thread per boundary slot: the slot that opens a run of equal rows folds the run in slot order, head by head.  A run
 // longer than kShortRun slots (a hub row that spans hundreds of chunks) would make that one thread a serial chain of
 // dependent loads, so its opener only records the slot; LongRunKernel folds those runs with a whole thread block each.
-constexpr int kShortRun = 32;
+constexpr int kShortRun = 4;
 constexpr int kMaxLongRuns = 1 << 16;
 
 __global__ void __launch_bounds__(kThreads) MergeBoundaryKernel(const LseParams p)
@@ -171,6 +173,21 @@ __global__ void __launch_bounds__(kThreads) MergeBoundaryKernel(const LseParams 
         }
         last = next;
     }
+    if (p.heads % 2 == 0) {  // two heads per 16-byte load: (max, sum, max, sum); the workspace is 256-byte aligned
+        for (int head = 0; head < p.heads; head += 2) {
+            float4 state = *reinterpret_cast<const float4*>(p.bound_state + (slot * p.heads + head) * 2);
+            for (int64_t next = slot + 1; next <= last; ++next) {
+                if (p.bound_row[next] == row) {
+                    const float4 other = *reinterpret_cast<const float4*>(p.bound_state + (next * p.heads + head) * 2);
+                    csr::LseMerge(state.x, state.y, other.x, other.y);
+                    csr::LseMerge(state.z, state.w, other.z, other.w);
+                }
+            }
+            p.lse[row * p.heads + head] = state.y == 0.0f ? state.x : state.x + __logf(state.y);
+            p.lse[row * p.heads + head + 1] = state.w == 0.0f ? state.z : state.z + __logf(state.w);
+        }
+        return;
+    }
     for (int head = 0; head < p.heads; ++head) {
         float m = p.bound_state[(slot * p.heads + head) * 2];
         float s = p.bound_state[(slot * p.heads + head) * 2 + 1];
@@ -183,25 +200,25 @@ __global__ void __launch_bounds__(kThreads) MergeBoundaryKernel(const LseParams 
     }
 }
 
-// One thread block per long run: walker w (a warp lane group of `lanes` threads, one head each) takes slots
-// slot + w, slot + w + walkers, ...; the walkers' states are then folded through shared memory in walker order, so the
-// result does not depend on scheduling.  The run's length is found once by a binary search (rows are sorted).
+// One warp per long run: the warp's 32 / lanes walkers (a walker = `lanes` lanes, one head each) take slots
+// slot + w, slot + w + walkers, ...; their states are then folded by shuffles in walker order, so the result does not
+// depend on scheduling.  The run's end is found once by a binary search over the chunks' first rows (rows are sorted).
 __global__ void __launch_bounds__(kThreads) LongRunKernel(const LseParams p)
 {
-    __shared__ float s_m[kThreads];
-    __shared__ float s_s[kThreads];
     const int64_t slots = p.chunks * 2;
     int64_t count = p.long_runs[0];
     count = count < kMaxLongRuns ? count : kMaxLongRuns;
-    const int head = threadIdx.x % p.lanes;
-    const int walker = threadIdx.x / p.lanes;
-    const int walkers = kThreads / p.lanes;
-    for (int64_t k = blockIdx.x; k < count; k += gridDim.x) {
+    const int lane = threadIdx.x & 31;
+    const int head = lane % p.lanes;
+    const int walker = lane / p.lanes;
+    const int walkers = 32 / p.lanes;
+    const int64_t warp = static_cast<int64_t>(blockIdx.x) * (kThreads / 32) + (threadIdx.x >> 5);
+    const int64_t warps = static_cast<int64_t>(gridDim.x) * (kThreads / 32);
+    for (int64_t k = warp; k < count; k += warps) {
         const int64_t slot = p.long_runs[1 + k];
         const int64_t row = p.bound_row[slot];
-        // A chunk inside a long run holds only this row: its first slot carries the row, its last slot is absent (-1).
-        // The run ends at the first slot whose row is larger; absent slots are skipped by looking at even slots only.
-        int64_t lo = (slot + 2) / 2, hi = p.chunks;  // chunk indices: first chunk whose first row exceeds `row`
+        // Inside a long run a chunk holds only this row: its first slot carries the row, its last slot is absent (-1).
+        int64_t lo = (slot + 2) / 2, hi = p.chunks;  // first chunk whose first row exceeds `row`
         while (lo < hi) {
             const int64_t mid = (lo + hi) >> 1;
             if (p.bound_row[mid * 2] <= row) {
@@ -210,25 +227,25 @@ __global__ void __launch_bounds__(kThreads) LongRunKernel(const LseParams p)
                 hi = mid;
             }
         }
-        const int64_t end = lo * 2;  // slots [slot, end) may belong to the run; the last chunk before `end` may end with another row
+        const int64_t end = lo * 2 < slots ? lo * 2 : slots;  // slots [slot, end) may belong to the run
         float m = -INFINITY, s = 0.0f;
         if (head < p.heads) {
-            for (int64_t next = slot + walker; next < end && next < slots; next += walkers) {
+            for (int64_t next = slot + walker; next < end; next += walkers) {
                 if (p.bound_row[next] == row) {
                     csr::LseMerge(m, s, p.bound_state[(next * p.heads + head) * 2], p.bound_state[(next * p.heads + head) * 2 + 1]);
                 }
             }
         }
-        s_m[threadIdx.x] = m;
-        s_s[threadIdx.x] = s;
-        __syncthreads();
-        if (walker == 0 && head < p.heads) {
-            for (int w = 1; w < walkers; ++w) {
-                csr::LseMerge(m, s, s_m[w * p.lanes + head], s_s[w * p.lanes + head]);
+        for (int w = 1; w < walkers; ++w) {  // walker 0 gathers the others in order
+            const float other_m = __shfl_sync(0xffffffffu, m, w * p.lanes + head);
+            const float other_s = __shfl_sync(0xffffffffu, s, w * p.lanes + head);
+            if (walker == 0) {
+                csr::LseMerge(m, s, other_m, other_s);
             }
+        }
+        if (walker == 0 && head < p.heads && row >= 0 && row < p.rows) {
             p.lse[row * p.heads + head] = s == 0.0f ? m : m + __logf(s);
         }
-        __syncthreads();
     }
 }
 
@@ -244,7 +261,7 @@ inline int64_t Chunks(int64_t nnz) { return CeilDiv(nnz, kChunk); }
 
 inline bool CheckDesc(const OpsgnnAttentionDesc* d)
 {
-    return d != nullptr && d->rows >= 0 && d->src_rows >= 0 && d->nnz >= 0 && d->heads >= 1 && d->heads <= 32 && d->width >= 1 &&
+    return d != nullptr && d->rows >= 0 && d->src_rows >= 0 && d->rows < 2147483647LL && d->src_rows < 2147483647LL && d->nnz >= 0 && d->heads >= 1 && d->heads <= 32 && d->width >= 1 &&
            (d->index_type == OPSGNN_I32 || d->index_type == OPSGNN_I64) && d->dtype == OPSGNN_F32;
 }
 
@@ -324,7 +341,7 @@ extern "C" int opsgnn_attention_lse(const OpsgnnAttentionDesc* desc, const void*
     }
     const unsigned merge_grid = static_cast<unsigned>(CeilDiv(p.chunks * 2, attention::kThreads));
     attention::MergeBoundaryKernel<<<merge_grid, attention::kThreads, 0, s>>>(p);
-    attention::LongRunKernel<<<static_cast<unsigned>(SmCount()) * 4, attention::kThreads, 0, s>>>(p);
+    attention::LongRunKernel<<<static_cast<unsigned>(SmCount()) * 8, attention::kThreads, 0, s>>>(p);
     return LaunchStatus();
 }
 
