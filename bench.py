@@ -203,14 +203,15 @@ def parse():
                         help="N > 1: staged = row stages whose pack + NCCL all-to-all overlap with the products of "
                              "earlier stages; staged_push = the same with the gather kernel storing into the peers' "
                              "symmetric memory; halo / pull = the unstaged forms; allgather = all of X every step; "
-                             "auto = staged")
-    parser.add_argument("--stages", default="0.2,0.25,0.3,0.25",
+                             "auto = staged_push between two GPUs, staged beyond (what measured fastest)")
+    parser.add_argument("--stages", default="0.1,0.2,0.3,0.4",
                         help="staged exchanges: shares of a shard's work per stage, in row order")
     parser.add_argument("--exchange-ctas", type=int, default=148,
                         help="staged exchanges: thread blocks of the pack / push kernel that runs beside the products")
     parser.add_argument("--row-cost", type=float, default=6.0, help="N > 1: cost of one output row in edges (shard balance)")
-    parser.add_argument("--e2e-row-cost", type=float, default=1.0,
-                        help="N > 1: the same for the host-buffer leg (measured at 4 GPUs: 272 ms per step with 1, 310 with 50)")
+    parser.add_argument("--e2e-row-cost", type=float, default=-1.0,
+                        help="N > 1: the same for the host-buffer leg; negative = pick, among a few candidates, the one whose "
+                             "busiest rank moves the fewest bytes over PCIe")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     parser.add_argument("--no-ops", action="store_true", help="skip the SDDMM / GAT legs, single-GPU and sharded (profiling runs)")
@@ -287,17 +288,18 @@ def main():
         sample = row_sample(my_ptr, my_col, my_val, lambda ids: x[ids], SHARD_SAMPLE_EDGES, base=bounds[rank])
         host_shard = None
         if not args.no_e2e:
-            # The host-buffer leg is bound by PCIe, not by the kernel: it gets its own shard bounds (balanced on edges +
-            # e2e_row_cost per row; weighing a row like the 50 edges its bytes amount to measured slower) and equal
-            # blocks of X.
-            e2e_bounds = balanced_row_bounds(rowptr, world, row_cost=args.e2e_row_cost)
+            # The host-buffer leg is bound by PCIe, not by the kernel: it gets its own shard bounds (balanced on the bytes
+            # every rank moves, see host_leg_bounds) and equal blocks of X.
+            e2e_bounds, e2e_choice = host_leg_bounds(rowptr, world, args.feat * elem, args.e2e_row_cost, balanced_row_bounds)
+            sharding["e2e_shards"] = e2e_choice
             block = nodes // world
             pieces = shard_csr(rowptr, col, value, e2e_bounds[rank], e2e_bounds[rank + 1])
             host_shard = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
                           for t in (*pieces, x[rank * block:(rank + 1) * block])]
             del pieces
         if args.exchange == "auto":
-            args.exchange = "staged"
+            # measured on this graph: 2 GPUs 22.6 (staged_push) / 24.4 (staged) / 25.5 ms (halo); 4 GPUs 18.7 / 17.6 / 18.8
+            args.exchange = "staged_push" if world == 2 else "staged"
         if args.exchange in ("halo", "pull", "staged", "staged_push"):
             # X is owned by the same row ranges as the output (a layer's output rows are the next layer's input)
             x_block = x[bounds[rank]:bounds[rank + 1]].clone()
@@ -676,6 +678,36 @@ def copy_rates(pinned, staging, out_host, out_like, sync):
     return rates
 
 
+def host_leg_bounds(rowptr, world, row_bytes, row_cost, balanced_row_bounds):
+    """Shard bounds of the host-buffer leg.  That leg is bound by the host side of PCIe: measured with four ranks copying
+    at once, a rank's uploads and downloads together ran at the rate of one direction alone (26 - 32 GB/s), so a rank's
+    step takes about (bytes up + bytes down) / that rate - up = its CSR slice + an equal block of X, down = its output
+    rows.  With a negative `row_cost` several shard balances are tried and the one whose busiest rank moves the fewest
+    bytes is taken (a pure function of the graph, so every rank picks the same)."""
+    rows = rowptr.numel() - 1
+
+    def busiest(bounds):
+        worst = 0
+        for k in range(world):
+            mine, edges = bounds[k + 1] - bounds[k], int(rowptr[bounds[k + 1]]) - int(rowptr[bounds[k]])
+            up = edges * 12 + (mine + 1) * 8 + (rows // world) * row_bytes  # col + weight per edge, pointers, block of X
+            down = mine * row_bytes
+            worst = max(worst, up + down)
+        return worst
+
+    if row_cost >= 0:
+        bounds = balanced_row_bounds(rowptr, world, row_cost=row_cost)
+        return bounds, {"row_cost": row_cost, "busiest_rank_bytes": busiest(bounds)}
+    best = None
+    for candidate in (1.0, 4.0, 12.0, 25.0, 51.0, 100.0, 400.0, 1e7):
+        bounds = balanced_row_bounds(rowptr, world, row_cost=candidate)
+        cost = busiest(bounds)
+        if best is None or cost < best[0]:
+            best = (cost, candidate, bounds)
+    return best[2], {"row_cost": best[1], "busiest_rank_bytes": best[0],
+                     "rule": "smallest maximum over ranks of upload + download bytes"}
+
+
 def host_available_bytes():
     try:
         with open("/proc/meminfo") as handle:
@@ -817,7 +849,7 @@ def end_to_end_sharded(args, pinned, nnz, dist, device, world):
     ms = float(elapsed.item()) / steps
     return {"value": nnz * args.feat / (ms * 1e-3), "unit": "nnz*feat/s", "ms_per_step": ms, "steps": steps,
             "h2d_bytes_per_step": int(in_bytes.item()), "d2h_bytes_per_step": int(out_bytes.item()),
-            "api": "ops_gnn.distributed.RowShardedSpmm", "shard_row_cost": args.e2e_row_cost, "rows_rank0": rows,
+            "api": "ops_gnn.distributed.RowShardedSpmm", "rows_rank0": rows,
             "overlap": "upload of step k+1 runs beside product and download of step k (2 staging sets, 3 streams)",
             "note": "bytes are summed over ranks; time is the max over ranks",
             "per_rank": gathered_rates,
