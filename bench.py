@@ -206,6 +206,8 @@ def parse():
                              "auto = staged_push between two GPUs, staged beyond (what measured fastest)")
     parser.add_argument("--stages", default="0.1,0.2,0.3,0.4",
                         help="staged exchanges: shares of a shard's work per stage, in row order")
+    parser.add_argument("--nccl-priority", type=int, default=1,
+                        help="N > 1, --exchange staged: 1 = the all-to-alls run in a NCCL group with a high-priority stream")
     parser.add_argument("--exchange-ctas", type=int, default=148,
                         help="staged exchanges: thread blocks of the pack / push kernel that runs beside the products")
     parser.add_argument("--row-cost", type=float, default=6.0, help="N > 1: cost of one output row in edges (shard balance)")
@@ -307,9 +309,17 @@ def main():
             torch.cuda.empty_cache()
             fractions = [float(f) for f in args.stages.split(",")]
 
+            exchange_group = None
+            if args.exchange == "staged" and args.nccl_priority:
+                from ops_gnn.distributed import high_priority_group
+
+                exchange_group = high_priority_group()
+                sharding["nccl_stream"] = "high priority"
+
             def build(kind):
                 if kind in ("staged", "staged_push"):
                     return StagedHaloSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device,
+                                          group=exchange_group if kind == "staged" else None,
                                           stage_fractions=fractions, row_cost=args.row_cost,
                                           transport="push" if kind == "staged_push" else "alltoall",
                                           exchange_ctas=args.exchange_ctas)

@@ -255,6 +255,9 @@ __device__ __forceinline__ int64_t ShuffleXor(int64_t v, int mask)
 }
 
 // ---- bulk-copy (TMA 1-D) ring ------------------------------------------------------------------------------------
+#ifndef OPSGNN_PACKED_FMA
+#define OPSGNN_PACKED_FMA 1  // 0: scalar multiply-adds (comparison builds)
+#endif
 #ifndef OPSGNN_BULK_STAGES
 #define OPSGNN_BULK_STAGES 2
 #endif
@@ -364,6 +367,8 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
     constexpr int EB = BULK ? kBulkStageBytes / kRowBytes : TR::kEdgeBatch;
     constexpr bool kIdentity = std::is_same<ColT, Identity>::value;
     constexpr bool kHasArg = RK == kExtremum;
+    // sums in float with an even vector width fold two elements per instruction
+    constexpr bool kPackedFma = OPSGNN_PACKED_FMA && RK == kSum && std::is_same<typename Traits<T, O, PtrT, ColT, VEC, NV, RK>::A, float>::value && VEC % 2 == 0;
 
     __shared__ int s_end[kItemsPerCta + 1];
     __shared__ int32_t s_col[kItemsPerCta];  // col(e), clamped to the source rows (fewer than 2^31, checked on the host)
@@ -667,7 +672,8 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
         }
         const int n = (j1 - first < eb) ? j1 - first : eb;
         const int st = b % kBulkStages;
-        if (lane == 0) {
+        const bool leader = lane == 0;
+        if (leader) {
             if constexpr (GENERAL) {
                 MbarExpectTx(bar_addr + st * 8, static_cast<uint32_t>(n) * (seg_bytes + weight_row_bytes));
                 BulkLoad(weight_addr + static_cast<uint32_t>(st * kBulkWeightBytes), val + (a0 + first) * p.val_width,
@@ -679,13 +685,15 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
         if constexpr (kIdentity) {
             // Consecutive source rows: when a row segment is the whole row, the stage is one contiguous copy.
             if (p.tiles_per_batch == 1 && a0 + first + n <= p.src_rows) {
-                if (lane == 0) {
+                if (leader) {
                     BulkLoad(ring_addr + static_cast<uint32_t>(st * kBulkStageBytes), mat + (a0 + first) * K,
                              static_cast<uint32_t>(n) * seg_bytes, bar_addr + st * 8);
                 }
                 return;
             }
         }
+        // Lanes 0 .. n - 1 issue one copy each.  (One elected lane issuing the stage's copies in a row measured slower:
+        // F = 256 fp32 37.2 against 34.3 ms, bf16 26.0 against 23.7 ms, 12 more warp instructions per edge.)
         for (int r = lane; r < n; r += 32) {
             if (OPSGNN_GUARD(4, static_cast<int64_t>(s_col[first + r]) * K + kbase + TILE - 1, p.src_rows * K + TILE)) {
                 BulkLoad(ring_addr + static_cast<uint32_t>(st * kBulkStageBytes + r * row_bytes),
@@ -814,6 +822,24 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
                                 Unpack<A, T, VEC>(wv, ws);
                             }
                         }
+                        if constexpr (kPackedFma) {
+                            // Two products per instruction (fma.rn.f32x2): the same rounding as the scalar form.
+#pragma unroll
+                            for (int c = 0; c < VEC; c += 2) {
+                                const int q = v * VEC + c;
+                                float w0 = w, w1 = w;
+                                if constexpr (GENERAL) {
+                                    if (p.wide == 1) {
+                                        w0 = ws[c];
+                                        w1 = ws[c + 1];
+                                    }
+                                }
+                                const float2 sum = __ffma2_rn(make_float2(w0, w1), make_float2(xs[c], xs[c + 1]),
+                                                              make_float2(acc[q], acc[q + 1]));
+                                acc[q] = sum.x;
+                                acc[q + 1] = sum.y;
+                            }
+                        } else {
 #pragma unroll
                         for (int c = 0; c < VEC; ++c) {
                             const int q = v * VEC + c;
@@ -831,6 +857,7 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
                             } else {
                                 LseOffer(acc[q], aux[q], value);
                             }
+                        }
                         }
                     }
                 }
@@ -1255,7 +1282,9 @@ int LaunchShaped(const Params& p, cudaStream_t stream)
     static const bool bulk_allowed = std::getenv("OPSGNN_NO_BULK") == nullptr;
     const bool bulk = lean && bulk_allowed;
     if constexpr (sizeof(T) == 4 || sizeof(T) == 2) {
-        // Rows of 16 to 256 bytes (a power of two): several edges per warp instruction instead of idle lanes.
+        // Rows of 16 to 256 bytes (a power of two): several edges per warp instruction instead of idle lanes.  (512-byte
+        // rows through the same per-lane asynchronous copies measured slower than the bulk ring: bf16 F = 256 29.5
+        // against 23.7 ms, 91 against 68 warp instructions per edge.)
         const int64_t vectors = p.feat / kVec;
         if (bulk && vector_ok && vectors >= 1 && vectors <= 16 && (vectors & (vectors - 1)) == 0) {
             Params narrow = p;

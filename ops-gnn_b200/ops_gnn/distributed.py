@@ -49,6 +49,19 @@ def balanced_row_bounds(rowptr: torch.Tensor, parts: int, row_cost: float = 0.0)
     return bounds
 
 
+def high_priority_group(ranks: Optional[Sequence[int]] = None):
+    """A NCCL process group whose collectives are launched on a high-priority stream.
+
+    The staged exchange runs its all-to-alls beside the SpMM of an earlier stage.  The thread blocks of a collective
+    launched at default priority are handed out only once every block of the product launched before it has been, so
+    the exchange would start when that product is nearly over; at high priority they take the next slots that free up.
+    """
+    import torch.distributed as dist
+
+    options = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+    return dist.new_group(ranks=None if ranks is None else list(ranks), backend="nccl", pg_options=options)
+
+
 def shard_csr(rowptr: torch.Tensor, col: torch.Tensor, value: Optional[torch.Tensor], first: int,
               last: int) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
     """CSR slice of rows ``[first, last)`` with the pointers rebased to zero; columns stay global."""
@@ -472,6 +485,12 @@ class StagedHaloSpmm:
         # first, so the next stage's rows get on the wire while the current product computes.  Without it the small
         # exchange kernels queue behind the product's thread blocks and the stages run one after the other (measured).
         self.comm_stream = torch.cuda.Stream(device, priority=-1) if on_gpu else None
+        # The all-to-all transport packs on a stream of its own, into one send buffer per stage, so the pack of stage
+        # k + 1 runs beside the all-to-all of stage k instead of behind it (measured at eight GPUs with one stream:
+        # 4 x (0.9 ms pack + 2.2 ms all-to-all) in a row).
+        self.pack_stream = torch.cuda.Stream(device, priority=-1) if (on_gpu and transport == "alltoall") else None
+        self._packed = [self.compact.new_empty((int(rows.numel()), feat)) for rows in self.send_rows] \
+            if transport == "alltoall" else []
         self.timing = False       # set it to collect CUDA events per phase of the next step (see phase_ms)
         self._events = None
 
@@ -530,12 +549,15 @@ class StagedHaloSpmm:
             self._mark(f"pack{k}")
             self._stream_barrier()                  # every peer's stage-k rows have landed here too
         else:
-            packed = self.own_block.new_empty((self.send_rows[k].numel(), self.feat))
-            if packed.size(0):
-                self.gather_rows(self.own_block, self.send_rows[k], [packed], self.exchange_ctas)
-            self._mark(f"pack{k}")
-            self.dist.all_to_all_single(halo, packed, self.want_splits[k], self.give_splits[k], group=self.group)
+            if self.pack_stream is None:
+                self._pack_stage(k)
+            self.dist.all_to_all_single(halo, self._packed[k], self.want_splits[k], self.give_splits[k], group=self.group)
         self._mark(f"exchange{k}")
+
+    def _pack_stage(self, k: int) -> None:
+        if self._packed[k].size(0):
+            self.gather_rows(self.own_block, self.send_rows[k], [self._packed[k]], self.exchange_ctas)
+        self._mark(f"pack{k}")
 
     def __call__(self, x_block: torch.Tensor) -> torch.Tensor:
         if x_block.data_ptr() != self.own_block.data_ptr():
@@ -551,15 +573,26 @@ class StagedHaloSpmm:
                 first, last = self.stage_rows[k], self.stage_rows[k + 1]
                 self.spmm_into(self.stage_ptr[k], self.stage_col[k], self.stage_val[k], self.compact, out[first:last])
             return out
-        main, comm = torch.cuda.current_stream(), self.comm_stream
+        main, comm, pack = torch.cuda.current_stream(), self.comm_stream, self.pack_stream
         comm.wait_stream(main)                      # the block is in place; last step's products are enqueued before
-        landed = []
+        landed, packed = [], []
         with torch.cuda.stream(comm):
             self._mark("start")
+        if pack is not None and self.world > 1:
+            pack.wait_stream(main)                  # main has waited for last step's all-to-alls: the send buffers are free
+            with torch.cuda.stream(pack):
+                for k in range(stages):
+                    self._pack_stage(k)
+                    event = torch.cuda.Event()
+                    event.record(pack)
+                    packed.append(event)
+        with torch.cuda.stream(comm):
             if self.world > 1 and self.transport == "push":
                 self._stream_barrier()              # nobody still reads the halo this step overwrites
             for k in range(stages):
                 if self.world > 1:
+                    if packed:
+                        comm.wait_event(packed[k])
                     self._exchange_stage(k)
                 event = torch.cuda.Event()
                 event.record(comm)
