@@ -21,20 +21,22 @@ The line printed by rank 0 carries
                 wrong exchange shows; the verdicts are reduced over the ranks),
   cpu_baseline  the CPU oracle (vectorised restatement of the reference's golden) on a bounded row sample, all host
                 threads (N = 1 only),
-  ops           N = 1 only: the other half of the metric - `sddmm_csr` dot on BASELINE config 3 (nnz/s, roofline) - and
-                the GAT layer of config 5, measured by the functions of bench_ops.py after the timed SpMM,
+  ops           the other half of the metric after the timed SpMM: at N = 1 `sddmm_csr` dot on BASELINE config 3 (nnz/s,
+                roofline) and the GAT layer of config 5 by the functions of bench_ops.py; at N > 1 the sharded SDDMM and
+                the sharded fused GAT layer,
   clocks        SM clock and throttle reasons sampled by nvidia-smi during the timed region.
 
 N > 1 (torchrun, one rank per GPU; strong scaling: the graph is fixed): output rows are split into contiguous ranges
 of equal work (edges + 6 per row) and X is owned by the same row ranges.  Each step moves only the rows of X a shard
-references.  `--exchange staged` (the default) cuts every shard into consecutive row stages whose exchanges (pack +
-NCCL all-to-all) run back to back on a side stream while the products of earlier stages compute;
+references.  `--exchange staged` cuts every shard into consecutive row stages whose exchanges (packs on one stream,
+NCCL all-to-alls of a high-priority group on another) run while the products of earlier stages compute;
 `--exchange staged_push` is the same pipeline with the gather kernel storing the rows straight into the peers'
-symmetric-memory buffers instead of pack + NCCL; `--exchange halo` / `pull` are the unstaged forms (whole exchange,
-then the product); `--exchange allgather` all-gathers all of X.  `sharding.phases_ms` gives, for one extra step after
-the timed region, the time from the step's start to the end of every phase (max over ranks); the `x_resident` record
-times the local SpMM alone.  The host-buffer leg at N > 1 uses the all-gather form with its own shard bounds
-(`--e2e-row-cost`).
+symmetric-memory buffers; `--exchange staged_copy` moves the packed rows with copy-engine transfers;
+`--exchange halo` / `pull` are the unstaged forms (whole exchange, then the product); `--exchange allgather`
+all-gathers all of X.  The default picks what measured fastest at each N: staged_push at 2, staged up to 4, halo beyond.
+`sharding.phases_ms` gives, for one extra step after the timed region, the time from the step's start to the end of
+every phase (max over ranks); the `x_resident` record times the local SpMM alone.  The host-buffer leg at N > 1 uses
+the all-gather form with shard bounds balanced on the bytes every rank moves over PCIe (`--e2e-row-cost`).
 `--impl reference` times the reference's CPU algorithm (the oracle port) on the host cores for the same metric.
 """
 import argparse
@@ -199,13 +201,16 @@ def parse():
     parser.add_argument("--feat", type=int, default=256)
     parser.add_argument("--dtype", default="fp32", choices=("fp32", "bf16"))
     parser.add_argument("--exchange", default="auto",
-                        choices=("auto", "staged", "staged_push", "allgather", "halo", "pull"),
+                        choices=("auto", "staged", "staged_push", "staged_copy", "allgather", "halo", "pull"),
                         help="N > 1: staged = row stages whose pack + NCCL all-to-all overlap with the products of "
                              "earlier stages; staged_push = the same with the gather kernel storing into the peers' "
+                             "symmetric memory; staged_copy = packed rows moved by copy-engine transfers into the peers' "
                              "symmetric memory; halo / pull = the unstaged forms; allgather = all of X every step; "
-                             "auto = staged_push between two GPUs, staged beyond (what measured fastest)")
+                             "auto = staged_push between two GPUs, staged up to four, halo beyond (what measured fastest)")
     parser.add_argument("--stages", default="0.1,0.2,0.3,0.4",
                         help="staged exchanges: shares of a shard's work per stage, in row order")
+    parser.add_argument("--copy-streams", type=int, default=4,
+                        help="N > 1, --exchange staged_copy: streams the per-peer copies of a stage are spread over")
     parser.add_argument("--nccl-priority", type=int, default=1,
                         help="N > 1, --exchange staged: 1 = the all-to-alls run in a NCCL group with a high-priority stream")
     parser.add_argument("--exchange-ctas", type=int, default=148,
@@ -300,9 +305,11 @@ def main():
                           for t in (*pieces, x[rank * block:(rank + 1) * block])]
             del pieces
         if args.exchange == "auto":
-            # measured on this graph: 2 GPUs 22.6 (staged_push) / 24.4 (staged) / 25.5 ms (halo); 4 GPUs 18.7 / 17.6 / 18.8
-            args.exchange = "staged_push" if world == 2 else "staged"
-        if args.exchange in ("halo", "pull", "staged", "staged_push"):
+            # measured on this graph, ms per step: 2 GPUs 22.5 (staged_push) / 22.2 - 23.7 (staged_copy) / 24.4 (staged) /
+            # 25.5 (halo); 4 GPUs 18.7 / - / 17.6 / 18.8; 8 GPUs, three boxes: halo 12.4 - 15.1, staged 12.3 - 12.5 on the
+            # box where halo took 12.4, staged_copy 13.8 where halo took 15.1, staged_push 18.6 where halo took 13.7
+            args.exchange = "staged_push" if world == 2 else ("staged" if world <= 4 else "halo")
+        if args.exchange in ("halo", "pull", "staged", "staged_push", "staged_copy"):
             # X is owned by the same row ranges as the output (a layer's output rows are the next layer's input)
             x_block = x[bounds[rank]:bounds[rank + 1]].clone()
             del rowptr, col, value, x
@@ -310,23 +317,27 @@ def main():
             fractions = [float(f) for f in args.stages.split(",")]
 
             exchange_group = None
-            if args.exchange == "staged" and args.nccl_priority:
+            if args.exchange in ("staged", "staged_copy") and args.nccl_priority:
                 from ops_gnn.distributed import high_priority_group
 
-                exchange_group = high_priority_group()
-                sharding["nccl_stream"] = "high priority"
+                try:
+                    exchange_group = high_priority_group()
+                    sharding["nccl_stream"] = "high priority"
+                except (RuntimeError, AttributeError, TypeError) as exc:  # the option is missing in this torch build
+                    sharding["nccl_stream"] = f"default priority ({type(exc).__name__})"
 
             def build(kind):
-                if kind in ("staged", "staged_push"):
+                if kind in ("staged", "staged_push", "staged_copy"):
                     return StagedHaloSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device,
                                           group=exchange_group if kind == "staged" else None,
+                                          barrier_group=exchange_group if kind == "staged_copy" else None,
                                           stage_fractions=fractions, row_cost=args.row_cost,
-                                          transport="push" if kind == "staged_push" else "alltoall",
-                                          exchange_ctas=args.exchange_ctas)
+                                          transport={"staged": "alltoall", "staged_push": "push", "staged_copy": "copy"}[kind],
+                                          exchange_ctas=args.exchange_ctas, copy_streams=args.copy_streams)
                 return HaloShardedSpmm(my_ptr, my_col, my_val, bounds, args.feat, dtype, device,
                                        transport="pull" if kind == "pull" else "alltoall")
 
-            fallback = {"staged_push": "staged", "pull": "halo"}
+            fallback = {"staged_push": "staged", "staged_copy": "staged", "pull": "halo"}
             try:
                 sharded, failure = build(args.exchange), None
             except (RuntimeError, ImportError, AttributeError) as exc:  # symmetric memory unavailable on this box

@@ -27,6 +27,7 @@ at::Tensor UnifiedSpmmCsr(const at::Tensor& indptr, const at::Tensor& indices, c
 
 at::Tensor GatherRows(const at::Tensor& x, const at::Tensor& index, const at::Tensor& unit_ptr, const at::Tensor& out);
 void GatherRowsInto(const at::Tensor& x, const at::Tensor& index, const std::vector<at::Tensor>& outs, int64_t max_ctas);
+void CopyRowsAsync(const at::Tensor& src, const at::Tensor& dst);
 at::Tensor CsrSpmmInto(const at::Tensor& ptr, const at::Tensor& col, const std::optional<at::Tensor>& value,
                        const at::Tensor& x, const at::Tensor& out);
 at::Tensor SpmmWeightedCsr(const at::Tensor& indptr, const at::Tensor& indices, const at::Tensor& x,

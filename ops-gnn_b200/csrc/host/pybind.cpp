@@ -38,6 +38,8 @@ void BindSpmm(py::module_& m)
     m.def("gather_rows", opsgnn::Scoped(&GatherRows), py::arg("x"), py::arg("index"), py::arg("unit_ptr"), py::arg("out"),
           "out[i] = x[index[i]] through the CSR engine (unit_ptr = 0..n); not part of the reference binding",
           py::call_guard<py::gil_scoped_release>());
+    m.def("copy_rows_async", opsgnn::Scoped(&CopyRowsAsync), py::arg("src"), py::arg("dst"),
+          "dst <- src with one cudaMemcpyAsync on the current stream (copy engine; dst may be a peer's symmetric-memory block)");
     m.def("gather_rows_into", opsgnn::Scoped(&GatherRowsInto), py::arg("x"), py::arg("index"), py::arg("outs"), py::arg("max_ctas") = 0,
           "outs[s][i] = x[index[start_s + i]] with a capped grid; the outputs may be views of a peer's mapped buffer; not "
           "part of the reference binding",

@@ -402,6 +402,26 @@ void GatherRowsInto(const at::Tensor& x, const at::Tensor& index, const std::vec
                 api);
 }
 
+// dst <- src with one cudaMemcpyAsync on the current stream: both contiguous, same dtype and size, `dst` in this GPU's
+// memory or in a peer's block of symmetric memory.  The driver runs such a copy on a copy engine, so an exchange made
+// of these takes no SM slot from a product running beside it (one call per copy; no batched-copy API is used).
+void CopyRowsAsync(const at::Tensor& src, const at::Tensor& dst)
+{
+    const char* api = "copy_rows_async";
+    TORCH_CHECK(src.defined() && dst.defined() && src.device().is_cuda() && dst.device().is_cuda(), api,
+                ": src and dst must be CUDA tensors");
+    TORCH_CHECK(src.is_contiguous() && dst.is_contiguous() && src.scalar_type() == dst.scalar_type() &&
+                    src.numel() == dst.numel(),
+                api, ": src and dst must be contiguous with one dtype and size");
+    if (src.numel() == 0) {
+        return;
+    }
+    c10::cuda::CUDAGuard guard(src.device());
+    const cudaError_t status = cudaMemcpyAsync(dst.data_ptr(), src.const_data_ptr(), src.nbytes(), cudaMemcpyDeviceToDevice,
+                                               static_cast<cudaStream_t>(CurrentStream(src)));
+    TORCH_CHECK(status == cudaSuccess, api, ": ", cudaGetErrorString(status));
+}
+
 // out[r, :] = sum_e value[e] * x[col[e], :] written into a caller-provided `out` (a row range of a larger matrix is
 // fine: any contiguous [rows, K] view).  The staged sharded SpMM produces its output stage by stage with this; the
 // structure is trusted (it was validated when the shard was built), so no validation pass runs here.

@@ -394,6 +394,12 @@ class StagedHaloSpmm:
     the gather kernel writes each wanted row straight into the requesting peer's buffer with plain peer stores - the
     pack IS the transfer, no send buffer and no NCCL data path; stream-ordered one-element all-reduces mark "every
     peer's stage-k rows have landed" and, at the start of a step, "nobody still reads last step's buffers".
+    ``transport="copy"`` (CUDA only): the same symmetric buffers, but the rows are packed into a local send buffer per
+    stage and moved with one ``cudaMemcpyAsync`` per peer and stage (``_pybind.copy_rows_async``), which the driver
+    runs on the copy engines: the transfer takes no SM slot and no issue bandwidth from the product running beside it
+    (NCCL's all-to-all kernels and the pushing gather kernel both slowed down, and slowed the product, when they
+    overlapped it).  The same one-element all-reduces act as barriers; pass ``barrier_group`` (a
+    :func:`high_priority_group`) so that they are not queued behind the product's thread blocks.
 
     The exchange kernel is the bounded row gather (``_pybind.gather_rows_into``): one launch per stage serves every
     peer, and its grid is capped at ``exchange_ctas`` thread blocks, because it runs beside a product and is bound by
@@ -406,15 +412,17 @@ class StagedHaloSpmm:
     def __init__(self, rowptr, col, value, bounds: Sequence[int], feat: int, dtype, device, group=None,
                  stage_fractions: Sequence[float] = (0.25, 0.25, 0.25, 0.25), row_cost: float = 4.0,
                  transport: str = "alltoall", spmm_into: Optional[Callable] = None,
-                 gather_rows: Optional[Callable] = None, exchange_ctas: int = 148):
+                 gather_rows: Optional[Callable] = None, exchange_ctas: int = 148, barrier_group=None,
+                 copy_streams: int = 4):
         import torch.distributed as dist
 
         self.dist, self.group = dist, group
+        self.barrier_group = barrier_group if barrier_group is not None else group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if len(bounds) != self.world + 1:
             raise ValueError("bounds must hold one row range per rank")
-        if transport not in ("alltoall", "push"):
-            raise ValueError("transport must be 'alltoall' or 'push'")
+        if transport not in ("alltoall", "push", "copy"):
+            raise ValueError("transport must be 'alltoall', 'push' or 'copy'")
         self.transport, self.feat, self.dtype, self.device = transport, feat, dtype, device
         self.exchange_ctas = int(exchange_ctas)
         self.bounds = [int(b) for b in bounds]
@@ -469,7 +477,7 @@ class StagedHaloSpmm:
         self.stage_val = [None if value is None else value[cut[k]:cut[k + 1]] for k in range(stages)]
 
         total_rows = self.own_rows + self.halo_rows
-        if transport == "push":
+        if transport in ("push", "copy"):
             self._setup_push(total_rows)
         else:
             self.compact = torch.empty((total_rows, feat), dtype=dtype, device=device)
@@ -488,9 +496,15 @@ class StagedHaloSpmm:
         # The all-to-all transport packs on a stream of its own, into one send buffer per stage, so the pack of stage
         # k + 1 runs beside the all-to-all of stage k instead of behind it (measured at eight GPUs with one stream:
         # 4 x (0.9 ms pack + 2.2 ms all-to-all) in a row).
-        self.pack_stream = torch.cuda.Stream(device, priority=-1) if (on_gpu and transport == "alltoall") else None
-        self._packed = [self.compact.new_empty((int(rows.numel()), feat)) for rows in self.send_rows] \
-            if transport == "alltoall" else []
+        self.pack_stream = torch.cuda.Stream(device, priority=-1) if (on_gpu and transport != "push") else None
+        self._packed = [torch.empty((int(rows.numel()), feat), dtype=dtype, device=device) for rows in self.send_rows] \
+            if transport != "push" else []
+        self.copy_streams = [torch.cuda.Stream(device, priority=-1) for _ in range(max(1, int(copy_streams)))] \
+            if (on_gpu and transport == "copy") else []
+        if transport == "copy":
+            from . import _pybind
+
+            self._copy_rows = _pybind.copy_rows_async
         self.timing = False       # set it to collect CUDA events per phase of the next step (see phase_ms)
         self._events = None
 
@@ -526,10 +540,10 @@ class StagedHaloSpmm:
                 if count:                           # nobody asks itself, so the segments are exactly the peers' shares
                     block = self._handle.get_buffer(peer, (capacity, self.feat), self.dtype)
                     targets.append(block[theirs[peer]:theirs[peer] + count])
-            self._push.append(targets)
+            self._push.append(targets)              # in the order of send_rows[k]: consecutive slices of a packed stage
 
     def _stream_barrier(self) -> None:
-        self.dist.all_reduce(self._flag, group=self.group)  # ordered on the current stream; no host wait
+        self.dist.all_reduce(self._flag, group=self.barrier_group)  # ordered on the current stream; no host wait
 
     def exchange_rows(self) -> Tuple[int, int]:
         """(rows this rank sends, rows it receives) per step, over all stages."""
@@ -548,6 +562,8 @@ class StagedHaloSpmm:
                 self.gather_rows(self.own_block, self.send_rows[k], self._push[k], self.exchange_ctas)
             self._mark(f"pack{k}")
             self._stream_barrier()                  # every peer's stage-k rows have landed here too
+        elif self.transport == "copy":
+            self._stream_barrier()                  # the copies of stage k were joined into this stream by the caller
         else:
             if self.pack_stream is None:
                 self._pack_stage(k)
@@ -555,8 +571,8 @@ class StagedHaloSpmm:
         self._mark(f"exchange{k}")
 
     def _pack_stage(self, k: int) -> None:
-        if self._packed[k].size(0):
-            self.gather_rows(self.own_block, self.send_rows[k], [self._packed[k]], self.exchange_ctas)
+        if self._packed[k].size(0):     # a local gather, bound by HBM: the kernel's own grid (0), not the NVLink-sized cap
+            self.gather_rows(self.own_block, self.send_rows[k], [self._packed[k]], 0)
         self._mark(f"pack{k}")
 
     def __call__(self, x_block: torch.Tensor) -> torch.Tensor:
@@ -579,7 +595,7 @@ class StagedHaloSpmm:
         with torch.cuda.stream(comm):
             self._mark("start")
         if pack is not None and self.world > 1:
-            pack.wait_stream(main)                  # main has waited for last step's all-to-alls: the send buffers are free
+            pack.wait_stream(main)                  # main has waited for last step's exchanges: the send buffers are free
             with torch.cuda.stream(pack):
                 for k in range(stages):
                     self._pack_stage(k)
@@ -587,11 +603,15 @@ class StagedHaloSpmm:
                     event.record(pack)
                     packed.append(event)
         with torch.cuda.stream(comm):
-            if self.world > 1 and self.transport == "push":
+            if self.world > 1 and self.transport in ("push", "copy"):
                 self._stream_barrier()              # nobody still reads the halo this step overwrites
+            free = torch.cuda.Event()
+            free.record(comm)
             for k in range(stages):
                 if self.world > 1:
-                    if packed:
+                    if self.transport == "copy":
+                        self._copy_stage(k, packed[k], free, comm)
+                    elif packed:
                         comm.wait_event(packed[k])
                     self._exchange_stage(k)
                 event = torch.cuda.Event()
@@ -604,6 +624,21 @@ class StagedHaloSpmm:
             self._mark(f"product{k}")
         comm.wait_stream(main)                      # scratch allocated on either stream is not reused across the join
         return out
+
+    def _copy_stage(self, k: int, packed_ready, halo_free, comm) -> None:
+        """One copy-engine transfer per peer from the packed rows of stage ``k`` into the peers' buffers, spread over
+        the copy streams; ``comm`` then waits for all of them."""
+        at = 0
+        for n, target in enumerate(self._push[k]):
+            stream = self.copy_streams[n % len(self.copy_streams)]
+            stream.wait_event(packed_ready)
+            stream.wait_event(halo_free)
+            with torch.cuda.stream(stream):
+                self._copy_rows(self._packed[k][at:at + target.size(0)], target)
+                done = torch.cuda.Event()
+                done.record(stream)
+            comm.wait_event(done)
+            at += target.size(0)
 
     def phase_ms(self):
         """After a step run with ``timing = True`` (and a device synchronise): milliseconds from the step's start to the

@@ -63,7 +63,7 @@ def _worker(rank, world, port, result_dir):
         results[transport + "_exchange"] = op.exchange_rows()
     from ops_gnn.distributed import StagedHaloSpmm
 
-    for transport in ("alltoall", "push"):
+    for transport in ("alltoall", "push", "copy"):
         op = StagedHaloSpmm(ptr, c, v, bounds, x.size(1), x.dtype, device, stage_fractions=(0.3, 0.3, 0.4),
                             transport=transport)
         first = op(mine)
@@ -110,7 +110,7 @@ def test_sharded_spmm_two_gpus(tmp_path):
     rowptr, col, value, x = (t.to("cuda:0") for t in _graph())
     want = csr_spmm(rowptr, col, value, x, "sum").cpu()
     assert parts[0]["staged_alltoall_exchange"] == parts[0]["alltoall_exchange"]   # every remote row moves once
-    for form in ("allgather", "alltoall", "pull", "staged_alltoall", "staged_push"):
+    for form in ("allgather", "alltoall", "pull", "staged_alltoall", "staged_push", "staged_copy"):
         got = torch.cat([p[form] for p in parts], dim=0)
         assert got.shape == want.shape
         # shard boundaries do not move edges between rows and the kernel's order inside a row depends only on the
