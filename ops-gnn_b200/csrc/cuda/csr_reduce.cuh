@@ -775,7 +775,8 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
             }
             // One gathered edge (slot t of the batch) folded into the accumulators; t is a compile-time constant so
             // the batch registers are indexed statically.
-            auto consume = [&](auto slot) {
+            auto consume = [&](auto slot, auto rule_c) {
+                constexpr int kRule = decltype(rule_c)::value;  // the extremum rule, fixed per copy of the loop body
                 const int t = static_cast<int>(slot);  // compile-time for the register path, run-time for the ring
                 {
                     const int e = j + t;
@@ -853,7 +854,7 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
                                 acc[q] += w * value;
                             } else if constexpr (RK == kExtremum) {
                                 value = value * w;  // w == 1 leaves every value, NaN and infinity included, as it is
-                                ExtremumOffer<A, int>(acc[q], where[q], value, e, p.is_min, p.extremum);
+                                ExtremumOffer<A, int>(acc[q], where[q], value, e, p.is_min, kRule);
                             } else {
                                 LseOffer(acc[q], aux[q], value);
                             }
@@ -870,7 +871,7 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
             if (N >= t_end) {                                      \
                 break;                                             \
             }                                                      \
-            consume(std::integral_constant<int, N>{});             \
+            consume(std::integral_constant<int, N>{}, rule_c);     \
         }
             if constexpr (kAttention) {
                 if (p.attention && t_end > t_begin && att_row != i) {  // first edges of a new row in this warp
@@ -928,17 +929,21 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
                         }
                     }
                 }
-            } else if constexpr (NARROW) {
+            } else {
+            // The run is folded by one copy of the loop body per extremum rule (the rule is uniform over the launch), so
+            // the per-element update compiles against a constant rule instead of testing it for every element.
+            auto fold_run = [&](auto rule_c) {
+            if constexpr (NARROW) {
                 for (int tt = t_begin; tt < t_end; tt += groups) {
                     if (tt + grp < t_end) {
-                        consume(tt + grp);
+                        consume(tt + grp, rule_c);
                     }
                 }
             } else if constexpr (BULK && EB > 4) {
                 for (int t = t_begin; t < t_end; ++t) {
-                    consume(t);
+                    consume(t, rule_c);
                 }
-            } else
+            } else {
             switch (t_begin) {  // register path and four-row bulk stages: slots are compile-time, offsets immediates (six-row stages measured slower this way: bf16 F = 256 25.2 against 23.5 ms)
                 OPSGNN_SLOT(0)
                 OPSGNN_SLOT(1)
@@ -958,6 +963,27 @@ __global__ void __launch_bounds__(kThreads, BULK ? OPSGNN_SUM_BLOCKS_PER_SM : 2)
                 OPSGNN_SLOT(15)
                 default:
                     break;
+            }
+            }
+            };
+            if constexpr (RK == kExtremum) {
+                switch (p.extremum) {
+                    case OPSGNN_EXTREMUM_IGNORE_NAN:
+                        fold_run(std::integral_constant<int, OPSGNN_EXTREMUM_IGNORE_NAN>{});
+                        break;
+                    case OPSGNN_EXTREMUM_PROPAGATE_NAN:
+                        fold_run(std::integral_constant<int, OPSGNN_EXTREMUM_PROPAGATE_NAN>{});
+                        break;
+                    case OPSGNN_EXTREMUM_SEEDED:
+                        fold_run(std::integral_constant<int, OPSGNN_EXTREMUM_SEEDED>{});
+                        break;
+                    default:
+                        fold_run(std::integral_constant<int, OPSGNN_EXTREMUM_SEEDED_LAST>{});
+                        break;
+                }
+            } else {
+                fold_run(std::integral_constant<int, 0>{});
+            }
             }
 #undef OPSGNN_SLOT
             if (t_end > t_begin) {
