@@ -9,8 +9,9 @@ One step is: all-gather the blocks of ``X`` into this GPU's own memory, then run
 Peer memory: no load anywhere in this module is a multicast load, and NVLS / multicast binding is switched off for
 the symmetric-memory buffers.  The NCCL forms land remote rows in the rank's own HBM before the SpMM reads them.  The
 ``pull`` and ``push`` transports hand a peer's symmetric-memory block to this library's own gather kernel, as its
-source (``pull``: plain peer loads) or as its destination (``push``: plain peer stores); no library kernel of anybody
-else is ever given a peer pointer.
+source (``pull``: plain peer loads) or as its destination (``push``: plain peer stores); the ``copy`` transport
+writes into a peer's block with ``cudaMemcpyAsync`` (a copy-engine transfer from this GPU's memory, not a kernel).  No
+library kernel of anybody else is ever given a peer pointer.
 
 ``feature_chunks > 1`` splits ``X`` by columns into contiguous chunk-major blocks: the all-gather of chunk ``c + 1``
 runs on a side stream while the SpMM of chunk ``c`` computes, so the transfer hides behind the math tile by tile.
