@@ -220,3 +220,28 @@ def test_balanced_bounds_properties():
     assert by_work[1] > by_edges[1]
     work = [int(skewed[b] - skewed[a]) + (b - a) for a, b in zip(by_work, by_work[1:])]
     assert abs(work[0] - work[1]) <= 101
+
+
+def test_host_leg_bounds_pick_the_lightest_busiest_rank():
+    """The host-buffer leg of the bench balances its shards on the bytes a rank moves over PCIe: the automatic choice is
+    never worse than a fixed row cost, is a valid partition, and is a pure function of the graph."""
+    import importlib.util
+    import sys
+
+    sys.path.insert(0, PACKAGE_DIR)
+    from ops_gnn.distributed import balanced_row_bounds
+
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(os.path.dirname(PACKAGE_DIR), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    generator = torch.Generator().manual_seed(5)
+    degree = (torch.rand(50000, generator=generator) ** -0.8).long().clamp(max=4000).sort(descending=True).values
+    rowptr = torch.cat([torch.zeros(1, dtype=torch.int64), degree.cumsum(0)])
+    for world in (2, 4, 8):
+        bounds, choice = bench.host_leg_bounds(rowptr, world, 1024, -1.0, balanced_row_bounds)
+        again, _ = bench.host_leg_bounds(rowptr, world, 1024, -1.0, balanced_row_bounds)
+        assert bounds == again and bounds[0] == 0 and bounds[-1] == 50000 and len(bounds) == world + 1
+        assert all(a <= b for a, b in zip(bounds, bounds[1:]))
+        for fixed in (1.0, 51.0, 1e7):
+            _, other = bench.host_leg_bounds(rowptr, world, 1024, fixed, balanced_row_bounds)
+            assert choice["busiest_rank_bytes"] <= other["busiest_rank_bytes"]

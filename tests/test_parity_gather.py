@@ -85,3 +85,28 @@ def test_gather_out_contract_and_errors(cuda_device):
         ops_gnn.gather_coo(src.reshape(2, 2, 6), torch.zeros(3, 2, dtype=torch.int64, device=cuda_device))
     empty = ops_gnn.gather_csr(torch.empty(0, 6, device=cuda_device), torch.zeros(1, dtype=torch.int64, device=cuda_device))
     assert empty.shape == (0, 6)
+
+
+def test_copy_rows_async(cuda_device):
+    """`copy_rows_async` is one stream-ordered cudaMemcpyAsync: bit-exact, ordered after earlier work on the stream, and
+    it refuses mismatched or strided operands."""
+    import ops_gnn
+
+    copy = ops_gnn._pybind.copy_rows_async
+    src = torch.randn(4097, 96, device=cuda_device)
+    dst = torch.zeros(8200, 96, device=cuda_device)
+    side = torch.cuda.Stream(cuda_device)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        doubled = src * 2                       # produced on the side stream right before the copy reads it
+        copy(doubled, dst[100:4197])
+        copy(src[:0], dst[:0])                  # empty: nothing to do
+    torch.cuda.current_stream().wait_stream(side)
+    assert torch.equal(dst[100:4197], src * 2)
+    assert not dst[:100].any() and not dst[4197:].any()
+    with pytest.raises(RuntimeError):
+        copy(src, dst[:4096])                   # sizes differ
+    with pytest.raises(RuntimeError):
+        copy(src[:, :48], dst[:4097, :48])      # not contiguous
+    with pytest.raises(RuntimeError):
+        copy(src, torch.zeros(4097, 96, dtype=torch.float64, device=cuda_device))
