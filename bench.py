@@ -25,6 +25,7 @@ The line printed by rank 0 carries
                 roofline) and the GAT layer of config 5 by the functions of bench_ops.py; at N > 1 the sharded SDDMM and
                 the sharded fused GAT layer,
   clocks        SM clock and throttle reasons sampled by nvidia-smi during the timed region.
+  step_ms       min / median / max of the K single steps (rank 0), beside ms_per_step = timed region / K.
 
 N > 1 (torchrun, one rank per GPU; strong scaling: the graph is fixed): output rows are split into contiguous ranges
 of equal work (edges + 6 per row) and X is owned by the same row ranges.  Each step moves only the rows of X a shard
@@ -394,8 +395,11 @@ def main():
         sampler.start()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
+    marks = []
     for _ in range(args.steps):
         out = step()
+        marks.append(torch.cuda.Event(enable_timing=True))
+        marks[-1].record()             # one more event per step: shows how the K steps spread around their mean
     stop.record()
     barrier()
     clocks = sampler.stop() if sampler else None
@@ -403,6 +407,9 @@ def main():
     if distributed:
         dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
     ms_per_step = float(elapsed.item()) / args.steps
+    each = sorted(a.elapsed_time(b) for a, b in zip([start] + marks[:-1], marks))
+    step_spread = {"min": round(each[0], 3), "median": round(statistics.median(each), 3), "max": round(each[-1], 3),
+                   "note": "single steps on rank 0's stream; ms_per_step is the whole region / steps, max over ranks"}
     ops_gnn.check_device_status()      # a device-side wait that ran out would have left rows unwritten: fail loudly
 
     # ---- parity: rows of the timed product against the float64 CPU oracle -------------------------------------------------
@@ -465,7 +472,7 @@ def main():
         "data": "synthetic", "config": config, "sharding": sharding, "clocks": clocks, "parity_check": parity,
         # ReduceKernel + FixupKernel per product and per pack gather on every rank (plans are cached after warm-up);
         # NCCL's own kernels are not counted
-        "gpu_launches": args.steps * world * launches_per_step,
+        "gpu_launches": args.steps * world * launches_per_step, "step_ms": step_spread,
     }
 
     peaks = {}
