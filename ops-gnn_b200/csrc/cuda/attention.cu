@@ -131,6 +131,237 @@ template <class IndexT> __global__ void __launch_bounds__(kThreads, 4) EdgeLogit
     }
 }
 
+// The same sweep for 3 to 8 heads (LANES = 4 or 8 threads per chunk): the row and column ids of a trip of eight edges
+// are loaded once per chunk - lane g of the chunk's group loads edge g - and handed round with group-wide shuffles
+// instead of every head loading all of them, and the ids of the next trip are in flight while this one is processed.
+// Lanes beyond the head count and groups beyond the last chunk run along (shuffles name the whole group) and write
+// nothing.  The order in which a head sees its edges, and therefore every result, is that of the kernel above.
+template <class IndexT, int LANES> __global__ void __launch_bounds__(kThreads, 4) EdgeLogitLseTeamKernel(const LseParams p)
+{
+    static_assert(LANES == 4 || LANES == 8, "a trip of eight edges is split over the group");
+    constexpr int kTrip = 8;
+    constexpr int kPer = kTrip / LANES;  // ids a lane loads per trip
+    const int64_t thread = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    const int64_t chunk_of_thread = thread / LANES;
+    const int head = static_cast<int>(thread - chunk_of_thread * LANES);
+    const bool live = chunk_of_thread < p.chunks;
+    const int64_t chunk = live ? chunk_of_thread : p.chunks - 1;  // an idle group shadows the last chunk
+    const bool writes = live && head < p.heads;
+    const int h = head < p.heads ? head : p.heads - 1;
+    const int group_lane = (threadIdx.x & 31) & ~(LANES - 1);
+    const unsigned group = ((LANES == 32 ? 0u : (1u << LANES)) - 1u) << group_lane;
+    const IndexT* __restrict__ edge_rows = static_cast<const IndexT*>(p.edge_rows);
+    const IndexT* __restrict__ col = static_cast<const IndexT*>(p.col);
+    const int64_t e0 = chunk * kChunk;
+    const int64_t e1 = (e0 + kChunk < p.nnz) ? e0 + kChunk : p.nnz;
+    auto load_ids = [&](int64_t base, int (&rows_of)[kPer], int (&cols_of)[kPer]) {
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            int64_t e = base + head + k * LANES;
+            e = e < e1 ? e : e1 - 1;
+            const int64_t row_id = static_cast<int64_t>(__ldg(edge_rows + e));
+            int64_t column = static_cast<int64_t>(__ldg(col + e));
+            column = column < 0 ? 0 : (column >= p.src_rows ? p.src_rows - 1 : column);  // validated upstream; never fault
+            rows_of[k] = static_cast<int>(row_id < 0 ? -1 : (row_id >= p.rows ? p.rows : row_id));
+            cols_of[k] = static_cast<int>(column);
+        }
+    };
+    int next_rows[kPer], next_cols[kPer];
+    load_ids(e0, next_rows, next_cols);
+    const int64_t first_id = static_cast<int64_t>(__ldg(edge_rows + e0));
+    const int first_row = static_cast<int>(first_id < 0 ? -1 : (first_id >= p.rows ? p.rows : first_id));
+    int row = first_row;
+    float bias = (row >= 0 && row < p.rows) ? __ldg(p.left + static_cast<int64_t>(row) * p.heads + h) : 0.0f;
+    float m = -INFINITY, s = 0.0f;
+    bool first_done = false;
+    float* state = p.bound_state + (chunk * 2) * p.heads * 2 + h * 2;
+    for (int64_t base = e0; base < e1; base += kTrip) {
+        int my_rows[kPer], my_cols[kPer];
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            my_rows[k] = next_rows[k];
+            my_cols[k] = next_cols[k];
+        }
+        if (base + kTrip < e1) {
+            load_ids(base + kTrip, next_rows, next_cols);
+        }
+        float v[kTrip];
+#pragma unroll
+        for (int u = 0; u < kTrip; ++u) {
+            const int column = __shfl_sync(group, my_cols[u / LANES], group_lane + (u % LANES));
+            v[u] = __ldg(p.right + static_cast<int64_t>(column) * p.heads + h);
+        }
+#pragma unroll
+        for (int u = 0; u < kTrip; ++u) {
+            const int r = __shfl_sync(group, my_rows[u / LANES], group_lane + (u % LANES));  // by every lane of the group
+            if (base + u < e1) {
+                if (r != row) {  // the current row ends here
+                    if (!first_done) {
+                        if (writes) {
+                            state[0] = m;  // first row of the chunk: may have begun in an earlier chunk
+                            state[1] = s;
+                        }
+                        first_done = true;
+                    } else if (writes && row >= 0 && row < p.rows) {
+                        p.lse[static_cast<int64_t>(row) * p.heads + h] = s == 0.0f ? m : m + __logf(s);
+                    }
+                    row = r;
+                    bias = (row >= 0 && row < p.rows) ? __ldg(p.left + static_cast<int64_t>(row) * p.heads + h) : 0.0f;
+                    m = -INFINITY;
+                    s = 0.0f;
+                }
+                float logit = bias + v[u];
+                logit = logit > 0.0f ? logit : logit * p.slope;
+                if (writes) {
+                    p.logits[(base + u) * p.heads + h] = logit;
+                }
+                Offer(m, s, logit);
+            }
+        }
+    }
+    if (!writes) {
+        return;
+    }
+    float* tail = state + p.heads * 2;
+    if (!first_done) {
+        state[0] = m;
+        state[1] = s;
+        tail[0] = -INFINITY;
+        tail[1] = 0.0f;
+    } else {
+        tail[0] = m;
+        tail[1] = s;
+    }
+    if (head == 0) {
+        p.bound_row[chunk * 2] = first_id;
+        p.bound_row[chunk * 2 + 1] = first_done ? row : -1;
+    }
+}
+
+// Eight heads, 16-byte aligned operands: two threads per chunk, four heads each, so that every gather, store and bias
+// load moves 16 bytes per lane (a warp instruction covers 16 chunks x 32 bytes instead of 4) - the sweep is bound by
+// the bytes it keeps in flight, and this quadruples them per instruction.  Ids are shared and prefetched as in the
+// team kernel; the order in which a head sees its edges is unchanged.
+template <class IndexT> __global__ void __launch_bounds__(kThreads, 3) EdgeLogitLseQuadKernel(const LseParams p)
+{
+    constexpr int kTrip = 8;
+    constexpr int kGroup = 2;            // lanes per chunk
+    constexpr int kPer = kTrip / kGroup;  // ids a lane loads per trip
+    const int64_t thread = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+    const int64_t chunk_of_thread = thread / kGroup;
+    const int half = static_cast<int>(thread - chunk_of_thread * kGroup);
+    const bool writes = chunk_of_thread < p.chunks;
+    const int64_t chunk = writes ? chunk_of_thread : p.chunks - 1;  // an idle pair shadows the last chunk
+    const int group_lane = (threadIdx.x & 31) & ~(kGroup - 1);
+    const unsigned group = 3u << group_lane;
+    const IndexT* __restrict__ edge_rows = static_cast<const IndexT*>(p.edge_rows);
+    const IndexT* __restrict__ col = static_cast<const IndexT*>(p.col);
+    const float4* __restrict__ left = reinterpret_cast<const float4*>(p.left);
+    const float4* __restrict__ right = reinterpret_cast<const float4*>(p.right);
+    float4* __restrict__ logits = reinterpret_cast<float4*>(p.logits);
+    const int64_t e0 = chunk * kChunk;
+    const int64_t e1 = (e0 + kChunk < p.nnz) ? e0 + kChunk : p.nnz;
+    auto load_ids = [&](int64_t base, int (&rows_of)[kPer], int (&cols_of)[kPer]) {
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            int64_t e = base + half + k * kGroup;
+            e = e < e1 ? e : e1 - 1;
+            const int64_t row_id = static_cast<int64_t>(__ldg(edge_rows + e));
+            int64_t column = static_cast<int64_t>(__ldg(col + e));
+            column = column < 0 ? 0 : (column >= p.src_rows ? p.src_rows - 1 : column);  // validated upstream; never fault
+            rows_of[k] = static_cast<int>(row_id < 0 ? -1 : (row_id >= p.rows ? p.rows : row_id));
+            cols_of[k] = static_cast<int>(column);
+        }
+    };
+    auto finish = [](float m, float s) { return s == 0.0f ? m : m + __logf(s); };
+    int next_rows[kPer], next_cols[kPer];
+    load_ids(e0, next_rows, next_cols);
+    const int64_t first_id = static_cast<int64_t>(__ldg(edge_rows + e0));
+    int row = static_cast<int>(first_id < 0 ? -1 : (first_id >= p.rows ? p.rows : first_id));
+    const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 bias = (row >= 0 && row < p.rows) ? __ldg(left + static_cast<int64_t>(row) * 2 + half) : zero;
+    float m[4], s[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        m[q] = -INFINITY;
+        s[q] = 0.0f;
+    }
+    bool first_done = false;
+    float4* state = reinterpret_cast<float4*>(p.bound_state + (chunk * 2) * 16 + half * 8);  // [chunk][first/last][8 heads][2]
+    for (int64_t base = e0; base < e1; base += kTrip) {
+        int my_rows[kPer], my_cols[kPer];
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            my_rows[k] = next_rows[k];
+            my_cols[k] = next_cols[k];
+        }
+        if (base + kTrip < e1) {
+            load_ids(base + kTrip, next_rows, next_cols);
+        }
+        float4 v[kTrip];
+#pragma unroll
+        for (int u = 0; u < kTrip; ++u) {
+            const int column = __shfl_sync(group, my_cols[u / kGroup], group_lane + (u % kGroup));
+            v[u] = __ldg(right + static_cast<int64_t>(column) * 2 + half);
+        }
+#pragma unroll
+        for (int u = 0; u < kTrip; ++u) {
+            const int r = __shfl_sync(group, my_rows[u / kGroup], group_lane + (u % kGroup));  // by both lanes of the pair
+            if (base + u < e1) {
+                if (r != row) {  // the current row ends here
+                    if (!first_done) {
+                        if (writes) {  // first row of the chunk: may have begun in an earlier chunk
+                            state[0] = make_float4(m[0], s[0], m[1], s[1]);
+                            state[1] = make_float4(m[2], s[2], m[3], s[3]);
+                        }
+                        first_done = true;
+                    } else if (writes && row >= 0 && row < p.rows) {
+                        reinterpret_cast<float4*>(p.lse)[static_cast<int64_t>(row) * 2 + half] =
+                            make_float4(finish(m[0], s[0]), finish(m[1], s[1]), finish(m[2], s[2]), finish(m[3], s[3]));
+                    }
+                    row = r;
+                    bias = (row >= 0 && row < p.rows) ? __ldg(left + static_cast<int64_t>(row) * 2 + half) : zero;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        m[q] = -INFINITY;
+                        s[q] = 0.0f;
+                    }
+                }
+                float4 logit = make_float4(bias.x + v[u].x, bias.y + v[u].y, bias.z + v[u].z, bias.w + v[u].w);
+                logit.x = logit.x > 0.0f ? logit.x : logit.x * p.slope;
+                logit.y = logit.y > 0.0f ? logit.y : logit.y * p.slope;
+                logit.z = logit.z > 0.0f ? logit.z : logit.z * p.slope;
+                logit.w = logit.w > 0.0f ? logit.w : logit.w * p.slope;
+                if (writes) {
+                    logits[(base + u) * 2 + half] = logit;
+                }
+                Offer(m[0], s[0], logit.x);
+                Offer(m[1], s[1], logit.y);
+                Offer(m[2], s[2], logit.z);
+                Offer(m[3], s[3], logit.w);
+            }
+        }
+    }
+    if (!writes) {
+        return;
+    }
+    // the last row of the chunk may continue in the next one; a chunk with a single row has only a first partial
+    float4* tail = state + 4;  // 8 heads x 2 floats further on
+    if (!first_done) {
+        state[0] = make_float4(m[0], s[0], m[1], s[1]);
+        state[1] = make_float4(m[2], s[2], m[3], s[3]);
+        tail[0] = make_float4(-INFINITY, 0.0f, -INFINITY, 0.0f);
+        tail[1] = make_float4(-INFINITY, 0.0f, -INFINITY, 0.0f);
+    } else {
+        tail[0] = make_float4(m[0], s[0], m[1], s[1]);
+        tail[1] = make_float4(m[2], s[2], m[3], s[3]);
+    }
+    if (half == 0) {
+        p.bound_row[chunk * 2] = first_id;
+        p.bound_row[chunk * 2 + 1] = first_done ? row : -1;
+    }
+}
+
 // One thread per boundary slot: the slot that opens a run of equal rows folds the run in slot order, head by head.  A run
 // longer than kShortRun slots (a hub row that spans hundreds of chunks) would make that one thread a serial chain of
 // dependent loads, so its opener only records the slot; LongRunKernel folds those runs with a warp each.
@@ -360,7 +591,27 @@ extern "C" int opsgnn_attention_lse(const OpsgnnAttentionDesc* desc, const void*
     p.bound_state = reinterpret_cast<float*>(cursor);
     const int64_t threads = p.chunks * p.lanes;
     const unsigned grid = static_cast<unsigned>(CeilDiv(threads, attention::kThreads));
-    if (desc->index_type == OPSGNN_I64) {
+    const bool wide = desc->index_type == OPSGNN_I64;
+    if (p.heads == 8 && Aligned(left, 16) && Aligned(right, 16) && Aligned(logits, 16) && Aligned(lse, 16)) {
+        const unsigned pairs = static_cast<unsigned>(CeilDiv(p.chunks * 2, attention::kThreads));
+        if (wide) {
+            attention::EdgeLogitLseQuadKernel<int64_t><<<pairs, attention::kThreads, 0, s>>>(p);
+        } else {
+            attention::EdgeLogitLseQuadKernel<int32_t><<<pairs, attention::kThreads, 0, s>>>(p);
+        }
+    } else if (p.lanes == 8) {
+        if (wide) {
+            attention::EdgeLogitLseTeamKernel<int64_t, 8><<<grid, attention::kThreads, 0, s>>>(p);
+        } else {
+            attention::EdgeLogitLseTeamKernel<int32_t, 8><<<grid, attention::kThreads, 0, s>>>(p);
+        }
+    } else if (p.lanes == 4) {
+        if (wide) {
+            attention::EdgeLogitLseTeamKernel<int64_t, 4><<<grid, attention::kThreads, 0, s>>>(p);
+        } else {
+            attention::EdgeLogitLseTeamKernel<int32_t, 4><<<grid, attention::kThreads, 0, s>>>(p);
+        }
+    } else if (wide) {
         attention::EdgeLogitLseKernel<int64_t><<<grid, attention::kThreads, 0, s>>>(p);
     } else {
         attention::EdgeLogitLseKernel<int32_t><<<grid, attention::kThreads, 0, s>>>(p);
