@@ -257,6 +257,16 @@ OPSGNN_API int opsgnn_attention_aggregate(const OpsgnnAttentionDesc* desc, const
                                           const float* lse, const void* x, void* out, const void* plan, void* workspace,
                                           int64_t workspace_bytes, void* stream);
 
+/* lse[groups, 8] = log-sum-exp per group of values[n, 8] (fp32, 16-byte aligned) under SORTED labels[n] in [0, groups):
+ * the edge sweep of the fused attention layer run over given values - chunks of 128 rows, four columns per thread,
+ * chunk partials folded in chunk order (deterministic).  Groups without rows get -inf.  No counterpart in the reference:
+ * it is the first pass of scatter_softmax / scatter_log_softmax / scatter_logsumexp for eight-column sources (per-head
+ * attention logits), whose rows are too narrow for the CSR engine's bulk ring
+ * (csrc/npu/scatter_softmax/op_kernel/common/scatter_softmax_kernel_phase.h:126-279 is the reference's form). */
+OPSGNN_API int opsgnn_sorted_lse8_workspace_bytes(int64_t n, int64_t* bytes);
+OPSGNN_API int opsgnn_sorted_lse8(const void* labels, int index_type, const float* values, float* lse, int64_t n, int64_t groups,
+                                  void* workspace, int64_t workspace_bytes, void* stream);
+
 /* dvalue[e, w] = sum_b sum_k mat[b, col[e], k] * grad[b, row(e), k]  (w = 0 when width == 1, else k).
  * Replaces TorchSparseSpmmValueGrad (csrc/npu/torch_sparse_spmm/op_kernel/arch35/torch_sparse_spmm_kernel.h:326-395).
  * mean == 1 divides by the row's edge count.  grad and out are fp32; mat has dtype mat_type. */

@@ -242,7 +242,11 @@ template <class IndexT, int LANES> __global__ void __launch_bounds__(kThreads, 4
 // load moves 16 bytes per lane (a warp instruction covers 16 chunks x 32 bytes instead of 4) - the sweep is bound by
 // the bytes it keeps in flight, and this quadruples them per instruction.  Ids are shared and prefetched as in the
 // team kernel; the order in which a head sees its edges is unchanged.
-template <class IndexT> __global__ void __launch_bounds__(kThreads, 3) EdgeLogitLseQuadKernel(const LseParams p)
+// FROM_VALUES = true is the same sweep over given values instead of logits to be formed: `right` is then a [nnz, 8]
+// matrix read in edge order (no columns, no bias, no activation, nothing written per edge) - the log-sum-exp per group
+// of narrow rows under sorted labels.
+template <class IndexT, bool FROM_VALUES = false>
+__global__ void __launch_bounds__(kThreads, 3) EdgeLogitLseQuadKernel(const LseParams p)
 {
     constexpr int kTrip = 8;
     constexpr int kGroup = 2;            // lanes per chunk
@@ -267,8 +271,11 @@ template <class IndexT> __global__ void __launch_bounds__(kThreads, 3) EdgeLogit
             int64_t e = base + half + k * kGroup;
             e = e < e1 ? e : e1 - 1;
             const int64_t row_id = static_cast<int64_t>(__ldg(edge_rows + e));
-            int64_t column = static_cast<int64_t>(__ldg(col + e));
-            column = column < 0 ? 0 : (column >= p.src_rows ? p.src_rows - 1 : column);  // validated upstream; never fault
+            int64_t column = 0;
+            if constexpr (!FROM_VALUES) {
+                column = static_cast<int64_t>(__ldg(col + e));
+                column = column < 0 ? 0 : (column >= p.src_rows ? p.src_rows - 1 : column);  // validated upstream; never fault
+            }
             rows_of[k] = static_cast<int>(row_id < 0 ? -1 : (row_id >= p.rows ? p.rows : row_id));
             cols_of[k] = static_cast<int>(column);
         }
@@ -279,7 +286,10 @@ template <class IndexT> __global__ void __launch_bounds__(kThreads, 3) EdgeLogit
     const int64_t first_id = static_cast<int64_t>(__ldg(edge_rows + e0));
     int row = static_cast<int>(first_id < 0 ? -1 : (first_id >= p.rows ? p.rows : first_id));
     const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    float4 bias = (row >= 0 && row < p.rows) ? __ldg(left + static_cast<int64_t>(row) * 2 + half) : zero;
+    float4 bias = zero;
+    if constexpr (!FROM_VALUES) {
+        bias = (row >= 0 && row < p.rows) ? __ldg(left + static_cast<int64_t>(row) * 2 + half) : zero;
+    }
     float m[4], s[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
@@ -301,8 +311,13 @@ template <class IndexT> __global__ void __launch_bounds__(kThreads, 3) EdgeLogit
         float4 v[kTrip];
 #pragma unroll
         for (int u = 0; u < kTrip; ++u) {
-            const int column = __shfl_sync(group, my_cols[u / kGroup], group_lane + (u % kGroup));
-            v[u] = __ldg(right + static_cast<int64_t>(column) * 2 + half);
+            if constexpr (FROM_VALUES) {
+                const int64_t e = base + u < e1 ? base + u : e1 - 1;
+                v[u] = __ldg(right + e * 2 + half);
+            } else {
+                const int column = __shfl_sync(group, my_cols[u / kGroup], group_lane + (u % kGroup));
+                v[u] = __ldg(right + static_cast<int64_t>(column) * 2 + half);
+            }
         }
 #pragma unroll
         for (int u = 0; u < kTrip; ++u) {
@@ -320,20 +335,25 @@ template <class IndexT> __global__ void __launch_bounds__(kThreads, 3) EdgeLogit
                             make_float4(finish(m[0], s[0]), finish(m[1], s[1]), finish(m[2], s[2]), finish(m[3], s[3]));
                     }
                     row = r;
-                    bias = (row >= 0 && row < p.rows) ? __ldg(left + static_cast<int64_t>(row) * 2 + half) : zero;
+                    if constexpr (!FROM_VALUES) {
+                        bias = (row >= 0 && row < p.rows) ? __ldg(left + static_cast<int64_t>(row) * 2 + half) : zero;
+                    }
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         m[q] = -INFINITY;
                         s[q] = 0.0f;
                     }
                 }
-                float4 logit = make_float4(bias.x + v[u].x, bias.y + v[u].y, bias.z + v[u].z, bias.w + v[u].w);
-                logit.x = logit.x > 0.0f ? logit.x : logit.x * p.slope;
-                logit.y = logit.y > 0.0f ? logit.y : logit.y * p.slope;
-                logit.z = logit.z > 0.0f ? logit.z : logit.z * p.slope;
-                logit.w = logit.w > 0.0f ? logit.w : logit.w * p.slope;
-                if (writes) {
-                    logits[(base + u) * 2 + half] = logit;
+                float4 logit = v[u];
+                if constexpr (!FROM_VALUES) {
+                    logit = make_float4(bias.x + v[u].x, bias.y + v[u].y, bias.z + v[u].z, bias.w + v[u].w);
+                    logit.x = logit.x > 0.0f ? logit.x : logit.x * p.slope;
+                    logit.y = logit.y > 0.0f ? logit.y : logit.y * p.slope;
+                    logit.z = logit.z > 0.0f ? logit.z : logit.z * p.slope;
+                    logit.w = logit.w > 0.0f ? logit.w : logit.w * p.slope;
+                    if (writes) {
+                        logits[(base + u) * 2 + half] = logit;
+                    }
                 }
                 Offer(m[0], s[0], logit.x);
                 Offer(m[1], s[1], logit.y);
@@ -615,6 +635,73 @@ extern "C" int opsgnn_attention_lse(const OpsgnnAttentionDesc* desc, const void*
         attention::EdgeLogitLseKernel<int64_t><<<grid, attention::kThreads, 0, s>>>(p);
     } else {
         attention::EdgeLogitLseKernel<int32_t><<<grid, attention::kThreads, 0, s>>>(p);
+    }
+    const unsigned merge_grid = static_cast<unsigned>(CeilDiv(p.chunks * 2, attention::kThreads));
+    attention::MergeBoundaryKernel<<<merge_grid, attention::kThreads, 0, s>>>(p);
+    attention::LongRunKernel<<<static_cast<unsigned>(SmCount()) * 8, attention::kThreads, 0, s>>>(p);
+    return LaunchStatus();
+}
+
+extern "C" int opsgnn_sorted_lse8_workspace_bytes(int64_t n, int64_t* bytes)
+{
+    if (n < 0 || bytes == nullptr) {
+        return OPSGNN_ERR_INVALID;
+    }
+    const int64_t chunks = attention::Chunks(n);
+    *bytes = AlignUp((1 + attention::kMaxLongRuns) * 8, 256) + AlignUp(chunks * 2 * 8, 256) + AlignUp(chunks * 2 * 8 * 2 * 4, 256);
+    return OPSGNN_OK;
+}
+
+extern "C" int opsgnn_sorted_lse8(const void* labels, int index_type, const float* values, float* lse, int64_t n, int64_t groups,
+                                  void* workspace, int64_t workspace_bytes, void* stream)
+{
+    if (n < 0 || groups < 0 || (index_type != OPSGNN_I32 && index_type != OPSGNN_I64)) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (groups == 0) {
+        return OPSGNN_OK;
+    }
+    if (lse == nullptr || !Aligned(lse, 16) || (n > 0 && (labels == nullptr || values == nullptr || !Aligned(values, 16)))) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (groups >= (int64_t(1) << 31)) {  // group ids travel as 32-bit values inside the sweep
+        return OPSGNN_ERR_LIMIT;
+    }
+    int64_t needed = 0;
+    opsgnn_sorted_lse8_workspace_bytes(n, &needed);
+    if (n > 0 && (workspace == nullptr || workspace_bytes < needed || !Aligned(workspace, 256))) {
+        return OPSGNN_ERR_WORKSPACE;
+    }
+    cudaStream_t s = AsStream(stream);
+    const int64_t cells = groups * 8;
+    int64_t fill_blocks = CeilDiv(cells, 256);
+    fill_blocks = fill_blocks < static_cast<int64_t>(SmCount()) * 8 ? fill_blocks : static_cast<int64_t>(SmCount()) * 8;
+    attention::FillKernel<<<static_cast<unsigned>(fill_blocks), 256, 0, s>>>(lse, -INFINITY, cells);  // groups without elements
+    if (n == 0) {
+        return LaunchStatus();
+    }
+    attention::LseParams p{};
+    p.edge_rows = labels;
+    p.right = values;
+    p.lse = lse;
+    p.nnz = n;
+    p.rows = groups;
+    p.src_rows = n;
+    p.chunks = attention::Chunks(n);
+    p.heads = 8;
+    p.lanes = 8;
+    char* cursor = static_cast<char*>(workspace);
+    p.long_runs = reinterpret_cast<int64_t*>(cursor);
+    OPSGNN_CUDA_TRY(cudaMemsetAsync(p.long_runs, 0, sizeof(int64_t), s));
+    cursor += AlignUp((1 + attention::kMaxLongRuns) * 8, 256);
+    p.bound_row = reinterpret_cast<int64_t*>(cursor);
+    cursor += AlignUp(p.chunks * 2 * 8, 256);
+    p.bound_state = reinterpret_cast<float*>(cursor);
+    const unsigned pairs = static_cast<unsigned>(CeilDiv(p.chunks * 2, attention::kThreads));
+    if (index_type == OPSGNN_I64) {
+        attention::EdgeLogitLseQuadKernel<int64_t, true><<<pairs, attention::kThreads, 0, s>>>(p);
+    } else {
+        attention::EdgeLogitLseQuadKernel<int32_t, true><<<pairs, attention::kThreads, 0, s>>>(p);
     }
     const unsigned merge_grid = static_cast<unsigned>(CeilDiv(p.chunks * 2, attention::kThreads));
     attention::MergeBoundaryKernel<<<merge_grid, attention::kThreads, 0, s>>>(p);

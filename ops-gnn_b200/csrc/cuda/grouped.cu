@@ -415,6 +415,7 @@ template <class T> __global__ void __launch_bounds__(kThreads) GradKernel(const 
 struct Layout {
     int64_t stats;       // floats per statistic array
     int64_t top_off, total_off, ptr_off, plan_off, carry_off, carry_bytes, total_bytes;
+    int64_t sweep_off, sweep_bytes;  // eight-column fp32 sources under sorted labels: the chunked sweep's boundary arrays
 };
 
 inline Layout MakeLayout(const OpsgnnGroupedDesc& d)
@@ -447,6 +448,11 @@ inline Layout MakeLayout(const OpsgnnGroupedDesc& d)
         opsgnn_csr_reduce_workspace_bytes(&r, &l.carry_bytes);
         l.carry_off = cursor;
         cursor += AlignUp(l.carry_bytes, 256);
+        if (d.batch == 1 && d.after == 8 && d.dtype == OPSGNN_F32) {
+            opsgnn_sorted_lse8_workspace_bytes(d.dim_len, &l.sweep_bytes);
+            l.sweep_off = cursor;
+            cursor += AlignUp(l.sweep_bytes, 256);
+        }
     }
     l.total_bytes = cursor;
     return l;
@@ -462,6 +468,33 @@ template <class T>
 int Forward(const OpsgnnGroupedDesc& d, Params p, char* workspace, const Layout& l, cudaStream_t s, const int64_t* perm = nullptr)
 {
     const int64_t n = d.batch * d.dim_len * d.after;
+    auto apply_lse = [&]() {  // second pass of the sorted forms: p.top holds the log-sum-exp of every group
+        if (d.mode == OPSGNN_GROUPED_LOGSUMEXP) {
+            CastKernel<T><<<Grid(l.stats), kThreads, 0, s>>>(p.top, static_cast<T*>(p.out), l.stats);
+        } else {
+            constexpr int kVec = 16 / sizeof(T);
+            if (d.batch == 1 && d.after % kVec == 0 && Aligned(p.src, 16) && Aligned(p.out, 16) && Aligned(p.top, 16)) {
+                ApplyLseVecKernel<T, kVec><<<Grid(n / kVec), kThreads, 0, s>>>(p);
+            } else {
+                ApplyLseKernel<T><<<Grid(n), kThreads, 0, s>>>(p);
+            }
+        }
+        return LaunchStatus();
+    };
+    if constexpr (std::is_same<T, float>::value) {
+        // Eight fp32 columns (per-head attention logits) under sorted labels: rows of 32 bytes are too narrow for the
+        // engine's ring (2.15 ms for 34.5M rows), so the first pass is the attention layer's chunked sweep over the
+        // values (no segment pointers, no plan).
+        if (d.sorted == 1 && perm == nullptr && n > 0 && l.stats > 0 && l.sweep_bytes > 0 && Aligned(p.src, 16) &&
+            Aligned(p.top, 16)) {
+            const int status = opsgnn_sorted_lse8(p.index, p.index64 ? OPSGNN_I64 : OPSGNN_I32, static_cast<const float*>(p.src),
+                                                  p.top, d.dim_len, d.groups, workspace + l.sweep_off, l.sweep_bytes, s);
+            if (status != OPSGNN_OK) {
+                return status;
+            }
+            return apply_lse();
+        }
+    }
     if (d.sorted && n > 0 && l.stats > 0) {
         int64_t* ptr = reinterpret_cast<int64_t*>(workspace + l.ptr_off);
         if (p.index64) {
@@ -507,17 +540,7 @@ int Forward(const OpsgnnGroupedDesc& d, Params p, char* workspace, const Layout&
         if (status != OPSGNN_OK) {
             return status;
         }
-        if (d.mode == OPSGNN_GROUPED_LOGSUMEXP) {
-            CastKernel<T><<<Grid(l.stats), kThreads, 0, s>>>(p.top, static_cast<T*>(p.out), l.stats);
-        } else {
-            constexpr int kVec = 16 / sizeof(T);
-            if (d.batch == 1 && d.after % kVec == 0 && Aligned(p.src, 16) && Aligned(p.out, 16) && Aligned(p.top, 16)) {
-                ApplyLseVecKernel<T, kVec><<<Grid(n / kVec), kThreads, 0, s>>>(p);
-            } else {
-                ApplyLseKernel<T><<<Grid(n), kThreads, 0, s>>>(p);
-            }
-        }
-        return LaunchStatus();
+        return apply_lse();
     }
     if (l.stats > 0) {
         FillKernel<<<Grid(l.stats), kThreads, 0, s>>>(p.top, -INFINITY, p.total, 0.0f, l.stats);

@@ -28,6 +28,7 @@ EXPORTS = (
     "opsgnn_csr_integer_mean", "opsgnn_sddmm_workspace_bytes", "opsgnn_sddmm_csr", "opsgnn_sddmm_csr_static",
     "opsgnn_spmm_value_grad",
     "opsgnn_attention_lse_workspace_bytes", "opsgnn_attention_lse", "opsgnn_attention_aggregate",
+    "opsgnn_sorted_lse8_workspace_bytes", "opsgnn_sorted_lse8",
     "opsgnn_gather_rows", "opsgnn_gather_expand",
     "opsgnn_ind2ptr", "opsgnn_ptr2ind", "opsgnn_csr_validate", "opsgnn_permute_values", "opsgnn_index_stats",
     "opsgnn_index_longest_run",
@@ -94,6 +95,8 @@ _PROTOTYPES = {
                                        c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "opsgnn_gather_rows": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_int, POINTER(c_int64),
                                    POINTER(c_void_p), c_int, c_void_p]),
+    "opsgnn_sorted_lse8_workspace_bytes": (c_int, [c_int64, POINTER(c_int64)]),
+    "opsgnn_sorted_lse8": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p]),
     "opsgnn_attention_lse_workspace_bytes": (c_int, [POINTER(AttentionDesc), POINTER(c_int64)]),
     "opsgnn_attention_lse": (c_int, [POINTER(AttentionDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_int64, c_void_p]),

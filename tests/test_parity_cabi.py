@@ -99,3 +99,33 @@ def test_gather_rows_entry_point(cuda_device):
     base = (ctypes.c_void_p * 1)(outs[1].data_ptr())
     assert lib.opsgnn_gather_rows(src.data_ptr(), index.data_ptr(), _cabi.I64, 6, 3000, 400, 1, bad, base, 0, stream) == -1
     assert lib.opsgnn_gather_rows(src.data_ptr(), index.data_ptr(), _cabi.I64, 5, 3000, 100, 1, bad, base, 0, stream) == -1
+
+
+def test_sorted_lse8_entry_point(cuda_device):
+    """opsgnn_sorted_lse8 through ctypes: log-sum-exp per group of an [n, 8] matrix under sorted labels (both index
+    dtypes, groups inside and across 128-row chunks, empty groups), against the float64 oracle; argument errors."""
+    from ops_gnn import _cabi
+
+    lib = _cabi.load()
+    gen = torch.Generator().manual_seed(41)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    lengths = torch.cat([torch.randint(0, 60, (2000,), generator=gen), torch.tensor([5000, 0, 1])])
+    labels = torch.repeat_interleave(torch.arange(lengths.numel()), lengths).contiguous()
+    n, groups = labels.numel(), lengths.numel()
+    values = torch.randn(n, 8, generator=gen) * 5
+    want = oracle.grouped_logsumexp_oracle(values, labels, 0, groups).float()
+    nbytes = ctypes.c_int64()
+    _cabi.check(lib.opsgnn_sorted_lse8_workspace_bytes(n, ctypes.byref(nbytes)), "sorted_lse8_workspace_bytes")
+    workspace = torch.empty(nbytes.value, dtype=torch.uint8, device=cuda_device)
+    d_values = values.to(cuda_device)
+    for index_dtype in (torch.int64, torch.int32):
+        d_labels = labels.to(index_dtype).to(cuda_device)
+        lse = torch.full((groups, 8), 7.0, device=cuda_device)
+        _cabi.check(lib.opsgnn_sorted_lse8(d_labels.data_ptr(), _cabi.torch_dtype_id(index_dtype), d_values.data_ptr(),
+                                           lse.data_ptr(), n, groups, workspace.data_ptr(), workspace.numel(), stream),
+                    "sorted_lse8")
+        assert_close(lse, want, what=f"sorted_lse8 {index_dtype}")
+    assert lib.opsgnn_sorted_lse8(d_labels.data_ptr(), _cabi.I32, d_values.data_ptr(), lse.data_ptr(), n, groups,
+                                  workspace.data_ptr(), 16, stream) == -3   # OPSGNN_ERR_WORKSPACE
+    assert lib.opsgnn_sorted_lse8(d_labels.data_ptr(), 99, d_values.data_ptr(), lse.data_ptr(), n, groups,
+                                  workspace.data_ptr(), workspace.numel(), stream) == -1

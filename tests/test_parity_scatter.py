@@ -124,6 +124,37 @@ def test_config2_softmax_sorted_and_shuffled(cuda_device):
                      oracle.grouped_logsumexp_oracle(values, labels, 0, groups).float(), what=name + " logsumexp")
 
 
+def test_eight_column_sorted_sources(cuda_device):
+    """[E, 8] fp32 sources under sorted labels (per-head attention logits) take the chunked sweep: groups inside one
+    128-row chunk, groups that straddle chunks, a hub group spanning hundreds of chunks that opens in the middle of a
+    chunk, empty groups, int32 labels, and the reference's +inf / -inf / NaN rules
+    (test/scatter_softmax/grouped_softmax_golden.py:50-86)."""
+    import ops_gnn
+
+    gen = torch.Generator().manual_seed(88)
+    lengths = torch.cat([torch.randint(0, 40, (3000,), generator=gen), torch.tensor([57, 40000, 0, 0, 3, 700, 129, 128, 1])])
+    index = torch.repeat_interleave(torch.arange(lengths.numel()), lengths).contiguous()
+    groups = lengths.numel() + 2                    # two more empty groups at the end
+    src = torch.randn(index.numel(), 8, generator=gen) * 4
+    first = int((index == 5).nonzero()[0]) if (index == 5).any() else 0
+    src[first, 0] = float("inf")                    # a group with +inf: softmax NaN, logsumexp +inf
+    where = (index == 9).nonzero().flatten()
+    if where.numel():
+        src[where, 1] = float("-inf")               # a column of a group all -inf: NaN / -inf
+    src[int((index == 3001).nonzero()[100]), 2] = float("nan")   # NaN inside the hub group
+    for labels in (index, index.to(torch.int32)):
+        d_src, d_index = src.to(cuda_device), labels.to(cuda_device)
+        assert_close(ops_gnn.scatter_logsumexp(d_src, d_index, 0, groups),
+                     oracle.grouped_logsumexp_oracle(src, index, 0, groups).float(), what="[E, 8] logsumexp")
+        assert_close(ops_gnn.scatter_softmax(d_src, d_index, 0, groups),
+                     oracle.grouped_softmax_oracle(src, index, 0, groups).float(), what="[E, 8] softmax")
+        assert_close(ops_gnn.scatter_log_softmax(d_src, d_index, 0, groups),
+                     oracle.grouped_softmax_oracle(src, index, 0, groups, log=True).float(), what="[E, 8] log_softmax")
+    twice = ops_gnn.scatter_softmax(src.to(cuda_device), index.to(cuda_device), 0, groups)
+    assert torch.equal(twice.isnan(), ops_gnn.scatter_softmax(src.to(cuda_device), index.to(cuda_device), 0, groups).isnan())
+    assert torch.equal(torch.nan_to_num(twice), torch.nan_to_num(ops_gnn.scatter_softmax(src.to(cuda_device), index.to(cuda_device), 0, groups)))
+
+
 def test_grouped_gradients(cuda_device):
     import ops_gnn
 
