@@ -386,6 +386,16 @@ OPSGNN_API int opsgnn_grouped_workspace_bytes(const OpsgnnGroupedDesc* desc, int
  * (logsumexp). */
 OPSGNN_API int opsgnn_grouped_forward(const OpsgnnGroupedDesc* desc, const void* src, const void* index, void* out,
                                       void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Sorted labels prepared once and reused: ptr[groups + 1] (the segment pointers of the label vector) and the CSR plan
+ * over them (opsgnn_csr_plan_bytes(groups, dim_len) bytes, 256-byte aligned).  opsgnn_grouped_forward_prepared is
+ * opsgnn_grouped_forward for desc->sorted = 1 without the boundary scan and the plan build; the workspace is sized by
+ * opsgnn_grouped_workspace_bytes as before.  No counterpart in the reference, which rescans the index in every call
+ * (csrc/npu/scatter_softmax/common/grouped_softmax_shared.h:178-208). */
+OPSGNN_API int opsgnn_grouped_prepare(const OpsgnnGroupedDesc* desc, const void* index, int64_t* ptr, void* plan, void* stream);
+OPSGNN_API int opsgnn_grouped_forward_prepared(const OpsgnnGroupedDesc* desc, const void* src, const void* index,
+                                               const int64_t* ptr, const void* plan, void* out, void* workspace,
+                                               int64_t workspace_bytes, void* stream);
 /* Softmax / log-softmax over an UNSORTED index through a permutation: perm[dim_len] (int64) must order the rows by group
  * (a stable argsort of index) and no group may hold more than OPSGNN_GROUPED_SHORT_GROUP rows.  Row perm[e] is read and
  * written in place of row e of the sorted sequence, so the result lands in the caller's row order with one read of src,

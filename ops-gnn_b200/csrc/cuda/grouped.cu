@@ -465,7 +465,8 @@ template <class T> bool ShortGroupShape(const OpsgnnGroupedDesc& d, const Params
 }
 
 template <class T>
-int Forward(const OpsgnnGroupedDesc& d, Params p, char* workspace, const Layout& l, cudaStream_t s, const int64_t* perm = nullptr)
+int Forward(const OpsgnnGroupedDesc& d, Params p, char* workspace, const Layout& l, cudaStream_t s, const int64_t* perm = nullptr,
+            const int64_t* ready_ptr = nullptr, const void* ready_plan = nullptr)
 {
     const int64_t n = d.batch * d.dim_len * d.after;
     auto apply_lse = [&]() {  // second pass of the sorted forms: p.top holds the log-sum-exp of every group
@@ -497,7 +498,9 @@ int Forward(const OpsgnnGroupedDesc& d, Params p, char* workspace, const Layout&
     }
     if (d.sorted && n > 0 && l.stats > 0) {
         int64_t* ptr = reinterpret_cast<int64_t*>(workspace + l.ptr_off);
-        if (p.index64) {
+        if (ready_ptr != nullptr) {  // prepared once for these labels: no boundary scan, no plan build
+            ptr = const_cast<int64_t*>(ready_ptr);
+        } else if (p.index64) {
             BoundaryKernel<int64_t><<<Grid(d.dim_len + 1), kThreads, 0, s>>>(static_cast<const int64_t*>(p.index), d.dim_len,
                                                                          ptr, d.groups, perm);
         } else {
@@ -520,9 +523,14 @@ int Forward(const OpsgnnGroupedDesc& d, Params p, char* workspace, const Layout&
             SegmentSoftmaxKernel<T, kVec><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p, ptr, perm, lanes);
             return LaunchStatus();
         }
-        int status = opsgnn_csr_plan_build(ptr, OPSGNN_I64, d.groups, d.dim_len, workspace + l.plan_off, s);
-        if (status != OPSGNN_OK) {
-            return status;
+        int status = OPSGNN_OK;
+        const void* plan = ready_plan;
+        if (plan == nullptr || ready_ptr == nullptr) {
+            status = opsgnn_csr_plan_build(ptr, OPSGNN_I64, d.groups, d.dim_len, workspace + l.plan_off, s);
+            if (status != OPSGNN_OK) {
+                return status;
+            }
+            plan = workspace + l.plan_off;
         }
         OpsgnnCsrReduceDesc r{};
         r.rows = d.groups;
@@ -535,8 +543,8 @@ int Forward(const OpsgnnGroupedDesc& d, Params p, char* workspace, const Layout&
         r.col_type = OPSGNN_I64;
         r.in_type = d.dtype;
         r.out_type = OPSGNN_F32;
-        status = opsgnn_csr_reduce(&r, ptr, nullptr, nullptr, p.src, p.top, nullptr, workspace + l.plan_off,
-                                   workspace + l.carry_off, l.carry_bytes, s);
+        status = opsgnn_csr_reduce(&r, ptr, nullptr, nullptr, p.src, p.top, nullptr, plan, workspace + l.carry_off,
+                                   l.carry_bytes, s);
         if (status != OPSGNN_OK) {
             return status;
         }
@@ -648,6 +656,70 @@ extern "C" int opsgnn_grouped_forward(const OpsgnnGroupedDesc* desc, const void*
             return Forward<__half>(d, p, static_cast<char*>(workspace), l, s);
         default:
             return Forward<__nv_bfloat16>(d, p, static_cast<char*>(workspace), l, s);
+    }
+}
+
+extern "C" int opsgnn_grouped_prepare(const OpsgnnGroupedDesc* desc, const void* index, int64_t* ptr, void* plan, void* stream)
+{
+    int status = CheckDesc(desc);
+    if (status != OPSGNN_OK) {
+        return status;
+    }
+    const OpsgnnGroupedDesc& d = *desc;
+    if (ptr == nullptr || plan == nullptr || (d.dim_len > 0 && index == nullptr) || !Aligned(plan, 256)) {
+        return OPSGNN_ERR_INVALID;
+    }
+    cudaStream_t s = AsStream(stream);
+    if (d.index_type == OPSGNN_I64) {
+        BoundaryKernel<int64_t><<<Grid(d.dim_len + 1), kThreads, 0, s>>>(static_cast<const int64_t*>(index), d.dim_len, ptr,
+                                                                     d.groups, nullptr);
+    } else {
+        BoundaryKernel<int32_t><<<Grid(d.dim_len + 1), kThreads, 0, s>>>(static_cast<const int32_t*>(index), d.dim_len, ptr,
+                                                                     d.groups, nullptr);
+    }
+    status = LaunchStatus();
+    if (status != OPSGNN_OK) {
+        return status;
+    }
+    return opsgnn_csr_plan_build(ptr, OPSGNN_I64, d.groups, d.dim_len, plan, s);
+}
+
+extern "C" int opsgnn_grouped_forward_prepared(const OpsgnnGroupedDesc* desc, const void* src, const void* index,
+                                               const int64_t* ptr, const void* plan, void* out, void* workspace,
+                                               int64_t workspace_bytes, void* stream)
+{
+    int status = CheckDesc(desc);
+    if (status != OPSGNN_OK) {
+        return status;
+    }
+    const OpsgnnGroupedDesc& d = *desc;
+    if (d.sorted != 1 || ptr == nullptr || plan == nullptr) {
+        return OPSGNN_ERR_INVALID;
+    }
+    const Layout l = MakeLayout(d);
+    const int64_t n = d.batch * d.dim_len * d.after;
+    const int64_t out_elems = d.mode == OPSGNN_GROUPED_LOGSUMEXP ? l.stats : n;
+    if (out_elems == 0) {
+        return OPSGNN_OK;
+    }
+    if (out == nullptr || (n > 0 && (src == nullptr || index == nullptr))) {
+        return OPSGNN_ERR_INVALID;
+    }
+    if (workspace == nullptr || workspace_bytes < l.total_bytes || !Aligned(workspace, 256)) {
+        return OPSGNN_ERR_WORKSPACE;
+    }
+    Params p = MakeParams(d, static_cast<char*>(workspace), l);
+    p.src = src;
+    p.index = index;
+    p.out = out;
+    cudaStream_t s = AsStream(stream);
+    switch (d.dtype) {
+        case OPSGNN_F32:
+            return Forward<float>(d, p, static_cast<char*>(workspace), l, s, nullptr, ptr, plan);
+        case OPSGNN_F16:
+            return Forward<__half>(d, p, static_cast<char*>(workspace), l, s, nullptr, ptr, plan);
+        default:
+            return Forward<__nv_bfloat16>(d, p, static_cast<char*>(workspace), l, s, nullptr, ptr, plan);
     }
 }
 

@@ -17,6 +17,11 @@ namespace {
 struct SortedEntry {
     TensorKey index;
     LabelFacts facts;
+    // Sorted labels: their segment pointers and the CSR plan over them, built on the first sorted forward call for
+    // `prepared_groups` groups and reused by later calls on the same stream (the tensors belong to that stream).
+    int64_t prepared_groups = -1;
+    void* prepared_stream = nullptr;
+    at::Tensor ptr, plan;
 };
 std::mutex g_sorted_mutex;
 std::list<SortedEntry> g_sorted;
@@ -78,6 +83,49 @@ LabelFacts LabelFactsOf(const at::Tensor& index, bool want_permutation)
 }
 
 namespace {
+
+// Segment pointers + plan of a sorted label vector from the facts cache, building them on a miss.  False when the
+// labels cannot be keyed (the caller then lets the kernel library scan them inside the call).
+bool PreparedSegments(const at::Tensor& index, const OpsgnnGroupedDesc& desc, at::Tensor* ptr, at::Tensor* plan)
+{
+    auto key = TensorKey::Of(index);
+    if (!key) {
+        return false;
+    }
+    void* stream = CurrentStream(index);
+    {
+        std::lock_guard<std::mutex> lock(g_sorted_mutex);
+        for (auto& entry : g_sorted) {
+            if (entry.index.Matches(*key)) {
+                if (entry.prepared_groups == desc.groups && entry.prepared_stream == stream && entry.ptr.defined()) {
+                    *ptr = entry.ptr;
+                    *plan = entry.plan;
+                    return true;
+                }
+                break;
+            }
+        }
+    }
+    int64_t plan_bytes = 0;
+    CheckStatus(opsgnn_csr_plan_bytes(desc.groups, desc.dim_len, &plan_bytes), "grouped");
+    at::Tensor made_ptr = at::empty({desc.groups + 1}, index.options().dtype(at::kLong));
+    at::Tensor made_plan = Scratch(plan_bytes, index);
+    CheckStatus(opsgnn_grouped_prepare(&desc, index.const_data_ptr(), made_ptr.data_ptr<int64_t>(), made_plan.data_ptr(), stream),
+                "grouped");
+    std::lock_guard<std::mutex> lock(g_sorted_mutex);
+    for (auto& entry : g_sorted) {
+        if (entry.index.Matches(*key)) {
+            entry.prepared_groups = desc.groups;
+            entry.prepared_stream = stream;
+            entry.ptr = made_ptr;
+            entry.plan = made_plan;
+            break;
+        }
+    }
+    *ptr = made_ptr;
+    *plan = made_plan;
+    return true;
+}
 
 struct View {
     int64_t batch, dim_len, after;
@@ -149,6 +197,16 @@ at::Tensor Forward(const at::Tensor& src, const at::Tensor& index, int64_t dim, 
         CheckStatus(opsgnn_grouped_forward_permuted(&desc, src.const_data_ptr(), index.const_data_ptr(),
                                                     facts.perm.const_data_ptr<int64_t>(), out.data_ptr(), scratch.data_ptr(),
                                                     scratch.numel(), CurrentStream(out)),
+                    api);
+        return out;
+    }
+    // Sorted labels through the engine (every shape but the eight-column sweep): pointers and plan come from the cache.
+    const bool sweep = v.batch == 1 && v.after == 8 && src.scalar_type() == at::kFloat;
+    at::Tensor ptr, plan;
+    if (facts.sorted && !sweep && index.numel() > 0 && PreparedSegments(index, desc, &ptr, &plan)) {
+        CheckStatus(opsgnn_grouped_forward_prepared(&desc, src.const_data_ptr(), index.const_data_ptr(),
+                                                    ptr.const_data_ptr<int64_t>(), plan.const_data_ptr(), out.data_ptr(),
+                                                    scratch.data_ptr(), scratch.numel(), CurrentStream(out)),
                     api);
         return out;
     }

@@ -29,6 +29,7 @@ EXPORTS = (
     "opsgnn_spmm_value_grad",
     "opsgnn_attention_lse_workspace_bytes", "opsgnn_attention_lse", "opsgnn_attention_aggregate",
     "opsgnn_sorted_lse8_workspace_bytes", "opsgnn_sorted_lse8",
+    "opsgnn_grouped_prepare", "opsgnn_grouped_forward_prepared",
     "opsgnn_gather_rows", "opsgnn_gather_expand",
     "opsgnn_ind2ptr", "opsgnn_ptr2ind", "opsgnn_csr_validate", "opsgnn_permute_values", "opsgnn_index_stats",
     "opsgnn_index_longest_run",
@@ -115,6 +116,9 @@ _PROTOTYPES = {
     "opsgnn_grouped_workspace_bytes": (c_int, [POINTER(GroupedDesc), POINTER(c_int64)]),
     "opsgnn_grouped_forward": (c_int, [POINTER(GroupedDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                        c_void_p]),
+    "opsgnn_grouped_prepare": (c_int, [POINTER(GroupedDesc), c_void_p, c_void_p, c_void_p, c_void_p]),
+    "opsgnn_grouped_forward_prepared": (c_int, [POINTER(GroupedDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                c_void_p, c_int64, c_void_p]),
     "opsgnn_grouped_forward_permuted": (c_int, [POINTER(GroupedDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                 c_int64, c_void_p]),
     "opsgnn_grouped_backward": (c_int, [POINTER(GroupedDesc), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -44,4 +44,8 @@ def scatter_logsumexp(src: torch.Tensor, index: torch.Tensor, dim: int = 0,
     dim = normalize_dim(dim, src.dim())
     check_inputs("scatter_logsumexp", src, index, dim)
     groups = resolve_groups(index, dim_size)
+    if not (torch.is_grad_enabled() and src.requires_grad) and src.numel() and src.is_contiguous() and index.is_contiguous():
+        # Nothing to differentiate: call the planner directly.  (An autograd node or a needless `.contiguous()` is a
+        # tensor operation, and any tensor operation makes the planner re-derive the index facts cached just above.)
+        return _pybind.scatter_logsumexp_forward(src, index, dim, groups)
     return _ScatterLogSumExp.apply(src, index, dim, groups)
