@@ -6,7 +6,7 @@ the count into an error.  The tests make the waits run out on a healthy GPU by s
 kernel then gives up before it looks at the barrier; copies already in flight are still awaited with the full limit
 before a block exits), check that the report arrives through the C ABI and through the Python API, and that the next
 launch with the default limit is correct again.  The reference states the same contract for its device kernels:
-a device error surfaces as a status the host reads (SURVEY of the reference: aclrtSynchronizeStream error codes).
+a device error surfaces as a status the host reads (the error code of its stream synchronisation after a launch).
 """
 import pytest
 import torch
